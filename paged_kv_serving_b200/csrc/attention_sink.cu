@@ -44,6 +44,7 @@ struct PrepareParams {
 template <typename A, typename C>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 qkv_prepare_kernel(A* __restrict__ qkv, const int32_t* __restrict__ positions, const float* __restrict__ freq,
+                   const float* __restrict__ q_weight, const float* __restrict__ k_weight,
                    const A* __restrict__ v_other, const float* __restrict__ lambda, A* __restrict__ v_keep,
                    C* __restrict__ k_pool, C* __restrict__ v_pool, const int32_t* __restrict__ slots, PrepareParams p,
                    int* __restrict__ status) {
@@ -86,12 +87,13 @@ qkv_prepare_kernel(A* __restrict__ qkv, const int32_t* __restrict__ positions, c
         sq = warp_sum(sq);
         inv = 1.0f / sqrtf(sq / (float)p.dim + p.eps);
       }
+      // (the norm's weight, one per coordinate and the same for every head, where the mixer has one)
       if (unit < p.n_heads) {
-        for (int d = lane; d < p.dim; d += 32) x[d] = from_float<A>(buf[d] * inv);
+        for (int d = lane; d < p.dim; d += 32) x[d] = from_float<A>(buf[d] * inv * (q_weight ? q_weight[d] : 1.0f));
       } else if (slot >= 0) {
         const int kvh = unit - p.n_heads;
         C* dst = k_pool + (((size_t)page * p.n_kv + kvh) * p.page_size + offset) * p.dim;
-        for (int d = lane; d < p.dim; d += 32) dst[d] = from_float<C>(buf[d] * inv);
+        for (int d = lane; d < p.dim; d += 32) dst[d] = from_float<C>(buf[d] * inv * (k_weight ? k_weight[d] : 1.0f));
       }
       __syncwarp();
     } else {
@@ -119,6 +121,11 @@ struct SinkParams {
   int window, keep_first;   // window 0: every earlier key is seen
   float scale, softcap;     // softcap 0: none
   int num_pages;
+  // per query head, each null or float32 [n_heads]: the score is multiplied by head_scale[h], and
+  // bias_a[h] * log(1 + bias_b[h] * (query position - key position)) is taken off it
+  const float* head_scale;
+  const float* bias_a;
+  const float* bias_b;
 };
 
 template <typename A, typename C>
@@ -203,7 +210,9 @@ attention_sink_kernel(const A* __restrict__ q, A* __restrict__ out, const C* __r
     const float* kr = k_s + lane * (dim + 1);
     for (int d = 0; d < dim; ++d) sc = fmaf(qr[d], kr[d], sc);
     sc *= p.scale;
+    if (p.head_scale) sc *= p.head_scale[head];
     if (p.softcap > 0.0f) sc = p.softcap * tanhf(sc / p.softcap);
+    if (p.bias_a) sc -= p.bias_a[head] * log1pf(p.bias_b[head] * (float)max(qpos - pos, 0));
     const bool ok = pos <= qpos && (pos >= my_lo || pos < keep);
     sc = ok ? sc : -INFINITY;
     const float tile_max = warp_max(sc);
@@ -273,6 +282,9 @@ struct SinkMmaParams {
   int num_splits;                      // > 1: blockIdx.z takes a share of the tile list and leaves its state in scratch
   float* part_o;                       // [T * H, splits, DV] unnormalised sums
   float* part_ml;                      // [T * H, splits, 2] maximum (log2 domain) and sum of weights
+  const float* head_scale;             // per query head, null or [n_heads]: a factor on the score
+  const float* bias_a;                 // per query head, null or [n_heads]: bias_a log(1 + bias_b distance) is taken off
+  const float* bias_b;
 };
 
 __device__ __forceinline__ uint32_t sm_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -389,6 +401,11 @@ __global__ void __launch_bounds__(SM_THREADS) attention_sink_mma_kernel(const Si
   const int warp_qpos_min = qpos_of(warp * 16);
   const int warp_qpos_max = min(qpos_of(warp * 16 + 15), key_hi - 1);
   const bool warp_active = warp * 16 < rows_valid;
+  // the two rows' own factors (log2 domain)
+  const int head_a = head_of(row_a), head_b = head_of(row_b);
+  const float hs_a = p.head_scale ? p.head_scale[head_a] : 1.0f, hs_b = p.head_scale ? p.head_scale[head_b] : 1.0f;
+  const float ba_a = p.bias_a ? p.bias_a[head_a] * 1.4426950408889634f : 0.0f, ba_b = p.bias_a ? p.bias_a[head_b] * 1.4426950408889634f : 0.0f;
+  const float bb_a = p.bias_a ? p.bias_b[head_a] : 0.0f, bb_b = p.bias_a ? p.bias_b[head_b] : 0.0f;
 
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
   float o[DTILES][4];
@@ -437,10 +454,12 @@ __global__ void __launch_bounds__(SM_THREADS) attention_sink_mma_kernel(const Si
       for (int i = 0; i < SM_BN / 8; ++i) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          float v = sc[i][e] * p.scale_log2;
-          if (p.cap_log2 > 0.0f) v = p.cap_log2 * (1.0f - 2.0f / (1.0f + exp2f(sc[i][e] * p.cap_x)));
+          const float raw = sc[i][e] * ((e < 2) ? hs_a : hs_b);
+          float v = raw * p.scale_log2;
+          if (p.cap_log2 > 0.0f) v = p.cap_log2 * (1.0f - 2.0f / (1.0f + exp2f(raw * p.cap_x)));
           const int kpos = base + i * 8 + 2 * t4 + (e & 1);
           const int qpos = (e < 2) ? qpos_a : qpos_b;
+          if (p.bias_a) v -= ((e < 2) ? ba_a : ba_b) * log1pf(((e < 2) ? bb_a : bb_b) * (float)max(qpos - kpos, 0));
           const bool ok = kpos <= qpos && (p.window == 0 || kpos > qpos - p.window || kpos < keep);
           v = ok ? v : -INFINITY;
           sc[i][e] = v;
@@ -546,22 +565,25 @@ __global__ void sink_mma_merge_kernel(const float* __restrict__ part_o, const fl
 using namespace pkv;
 
 template <typename A, typename C>
-static int launch_prepare(void* qkv, const int32_t* positions, const float* freq, const void* v_other, const float* lambda,
+static int launch_prepare(void* qkv, const int32_t* positions, const float* freq, const float* q_weight, const float* k_weight,
+                          const void* v_other, const float* lambda,
                           void* v_keep, void* k_pool, void* v_pool, const int32_t* slots, const PrepareParams& p, int tokens,
                           int* status, cudaStream_t s) {
   const size_t smem = (size_t)SK_WARPS * p.dim * sizeof(float);
   return launch_kernel(qkv_prepare_kernel<A, C>, dim3(tokens), dim3(SK_WARPS * 32), smem, s, true, 0, (A*)qkv, positions, freq,
-                       (const A*)v_other, lambda, (A*)v_keep, (C*)k_pool, (C*)v_pool, slots, p, status);
+                       q_weight, k_weight, (const A*)v_other, lambda, (A*)v_keep, (C*)k_pool, (C*)v_pool, slots, p, status);
 }
 
 // qkv [tokens, ld]: H query heads of `dim`, G key heads of `dim`, G value heads of `vdim`.
-// freq [rot_dims / 2] float32 (null with rot_dims 0). v_other: the values [tokens, ld_other] of
+// freq [rot_dims / 2] float32 (null with rot_dims 0). q_weight, k_weight: float32 [dim] factors on
+// the unit-norm query and key heads, or null. v_other: the values [tokens, ld_other] of
 // another layer to blend with, weight lambda[0] (a float on the device), or null. v_keep: where
 // to leave this layer's values [tokens, G * vdim] as they are cached, or null.
 // k_pool [pages][G][page_size][dim], v_pool [pages][G][page_size][vdim]; slots: int32 per token,
 // negative (or null): nothing is cached for it.
 PKV_EXPORT int pkv_qkv_prepare(void* qkv, int act_dtype, int ld, const int32_t* positions, const float* freq, int rot_dims,
-                               float rot_factor, float eps, int unit_norm, const void* v_other, int ld_other,
+                               float rot_factor, float eps, int unit_norm, const float* q_weight, const float* k_weight,
+                               const void* v_other, int ld_other,
                                const float* lambda, void* v_keep, void* k_pool, void* v_pool, int cache_dtype,
                                const int32_t* slots, long long pool_slots, int tokens, int n_heads, int n_kv, int dim, int vdim,
                                int page_size, int* status, void* stream) {
@@ -573,7 +595,7 @@ PKV_EXPORT int pkv_qkv_prepare(void* qkv, int act_dtype, int ld, const int32_t* 
   PrepareParams p{ld, n_heads, n_kv, dim, vdim, rot_dims, rot_factor, eps, unit_norm, page_size, pool_slots, ld_other};
   cudaStream_t s = (cudaStream_t)stream;
 #define PKV_PREP(A, C) \
-  return launch_prepare<A, C>(qkv, positions, freq, v_other, lambda, v_keep, k_pool, v_pool, slots, p, tokens, status, s)
+  return launch_prepare<A, C>(qkv, positions, freq, q_weight, k_weight, v_other, lambda, v_keep, k_pool, v_pool, slots, p, tokens, status, s)
   if (act_dtype == PKV_F32 && cache_dtype == PKV_F32) PKV_PREP(float, float);
   if (act_dtype == PKV_BF16 && cache_dtype == PKV_BF16) PKV_PREP(bf16, bf16);
   if (act_dtype == PKV_F32 && cache_dtype == PKV_BF16) PKV_PREP(float, bf16);
@@ -604,13 +626,15 @@ PKV_EXPORT int pkv_attention_sink(const void* q, int q_ld, void* out, int act_dt
                                   int cache_dtype, const int32_t* block_table, int table_stride, const int32_t* seq_starts,
                                   const int32_t* first_pos, const int32_t* work_seq, const int32_t* work_row0, int n_work,
                                   int n_heads, int n_kv, int dim, int vdim, int page_size, int window, int keep_first,
-                                  float scale, float softcap, int num_pages, int* status, void* stream) {
+                                  float scale, float softcap, const float* head_scale, const float* bias_a,
+                                  const float* bias_b, int num_pages, int* status, void* stream) {
   if (n_work <= 0) return 0;
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || dim <= 0 || vdim <= 0 || page_size <= 0 || window < 0 || keep_first < 0 ||
-      num_pages <= 0 || softcap < 0.0f)
+      num_pages <= 0 || softcap < 0.0f || (bias_a == nullptr) != (bias_b == nullptr))
     return PKV_ERR_SIZE;
   if (vdim > 32 * SK_MAX_ACC || dim > SK_MAX_DIM || n_kv > 65535) return PKV_ERR_LIMIT;
-  SinkParams p{q_ld, table_stride, n_heads, n_kv, dim, vdim, page_size, window, keep_first, scale, softcap, num_pages};
+  SinkParams p{q_ld, table_stride, n_heads, n_kv, dim, vdim, page_size, window, keep_first, scale, softcap, num_pages,
+               head_scale, bias_a, bias_b};
   cudaStream_t s = (cudaStream_t)stream;
 #define PKV_SINK(A, C) \
   return launch_sink<A, C>(q, out, k_pool, v_pool, block_table, seq_starts, first_pos, work_seq, work_row0, n_work, p, status, s)
@@ -649,20 +673,21 @@ PKV_EXPORT int pkv_attention_sink_mma(const void* q, int q_ld, void* out, const 
                                       const int32_t* block_table, int table_stride, const int32_t* seq_starts,
                                       const int32_t* first_pos, const int32_t* work_seq, const int32_t* work_q0, int n_work,
                                       int n_heads, int n_kv, int dk, int dv, int page_size, int window, int keep_first,
-                                      float scale, float softcap, int num_pages, int* status, int num_splits, float* part_o,
+                                      float scale, float softcap, const float* head_scale, const float* bias_a,
+                                      const float* bias_b, int num_pages, int* status, int num_splits, float* part_o,
                                       float* part_ml, long long tokens, void* stream) {
   if (n_work <= 0) return 0;
   if (!pkv_attention_sink_mma_supports(dk, dv, q_ld)) return PKV_ERR_LIMIT;
   if (num_splits < 1 || num_splits > 8 || (num_splits > 1 && (!part_o || !part_ml))) return PKV_ERR_SIZE;
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size <= 0 || window < 0 || keep_first < 0 || num_pages <= 0 ||
-      softcap < 0.0f || !(scale > 0.0f) || n_kv > 65535)
+      softcap < 0.0f || !(scale > 0.0f) || n_kv > 65535 || (bias_a == nullptr) != (bias_b == nullptr))
     return PKV_ERR_SIZE;
   if ((uintptr_t)q % 16 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16 || (uintptr_t)out % 4) return PKV_ERR_ALIGN;
   const float log2e = 1.4426950408889634f;
   SinkMmaParams p{(const bf16*)q, q_ld, (bf16*)out, (const bf16*)k_pool, (const bf16*)v_pool, block_table, table_stride,
                   seq_starts, first_pos, work_seq, work_q0, n_heads, n_kv, dk, page_size, window, keep_first, scale * log2e,
                   softcap * log2e, softcap > 0.0f ? 2.0f * scale / softcap * log2e : 0.0f, num_pages, status, num_splits, part_o,
-                  part_ml};
+                  part_ml, head_scale, bias_a, bias_b};
   cudaStream_t s = (cudaStream_t)stream;
   int rc = PKV_ERR_LIMIT;
   switch (dv) {

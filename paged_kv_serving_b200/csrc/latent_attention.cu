@@ -52,11 +52,13 @@ latent_prepare_kernel(const float* __restrict__ fused, int ld, int q_off, int q_
   const int t = blockIdx.x;
   const float* row = fused + (size_t)t * ld;
   float ss = 0.0f;
-  for (int i = threadIdx.x; i < q_rank; i += blockDim.x) ss = fmaf(row[q_off + i], row[q_off + i], ss);
-  ss = block_sum(ss, scratch);
-  const float q_inv = 1.0f / sqrtf(ss / (float)q_rank + eps);
-  for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
-    c_q[(size_t)t * q_rank + i] = from_float<C>(row[q_off + i] * q_inv * q_weight[i]);
+  if (q_rank > 0) {                                       // (0: the queries are not low-rank, there is no query latent)
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) ss = fmaf(row[q_off + i], row[q_off + i], ss);
+    ss = block_sum(ss, scratch);
+    const float q_inv = 1.0f / sqrtf(ss / (float)q_rank + eps);
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
+      c_q[(size_t)t * q_rank + i] = from_float<C>(row[q_off + i] * q_inv * q_weight[i]);
+  }
   const long long slot = slots ? slots[t] : -1;
   if (slot < 0) return;                                   // a stand-in token, or a call that does not write
   if (slot >= pool_rows) {
@@ -539,7 +541,7 @@ PKV_EXPORT int pkv_latent_prepare(const float* fused, int ld, int q_off, int q_r
                                   const int32_t* positions, const int32_t* slots, void* c_q, void* pool, int cache_dtype,
                                   long long pool_rows, int tokens, int* status, void* stream) {
   if (tokens <= 0) return 0;
-  if (q_rank < 1 || rank < 1 || rot < 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1)) return PKV_ERR_SIZE;
+  if (q_rank < 0 || (q_rank > 0 && !q_weight) || rank < 1 || rot < 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1)) return PKV_ERR_SIZE;
   const size_t smem = (size_t)(rot + 32) * sizeof(float);
   if (smem > 48 * 1024) return PKV_ERR_LIMIT;
   cudaStream_t s = (cudaStream_t)stream;

@@ -333,6 +333,14 @@ token_side_kernel(float* __restrict__ hidden, const D* __restrict__ delta, const
   for (int c = threadIdx.x; c < width; c += blockDim.x) out[(size_t)t * width + c] = y[c] * inv * norm_w[c];
 }
 
+// x <- cap * tanh(x / cap), in place (float32): a soft cap on logits.
+__global__ void softcap_kernel(float* __restrict__ x, long long total, float cap) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) x[i] = cap * tanhf(x[i] / cap);
+}
+
 }  // namespace pkv
 
 using namespace pkv;
@@ -499,4 +507,10 @@ PKV_EXPORT int pkv_token_side(float* hidden, const void* delta, int delta_dtype,
   if (dtype == PKV_F32 && d == PKV_BF16) PKV_TS(float, bf16);
 #undef PKV_TS
   return PKV_ERR_DTYPE;
+}
+
+PKV_EXPORT int pkv_softcap(float* x, long long total, float cap, void* stream) {
+  if (total <= 0) return 0;
+  if (!(cap > 0.0f)) return PKV_ERR_SIZE;
+  return launch_kernel(softcap_kernel, dim3(blocks_for(total, 256)), dim3(256), 0, (cudaStream_t)stream, true, 0, x, total, cap);
 }

@@ -26,7 +26,7 @@ from paged_kv_serving_b200.cache.pages import NULL_PAGE
 from paged_kv_serving_b200.engine.batch import BatchEntry, ExecutionBatch
 from paged_kv_serving_b200.engine.sequence import TableSnapshot
 from paged_kv_serving_b200.models.decoder import DecoderModel
-from paged_kv_serving_b200.ops import arena, gemm
+from paged_kv_serving_b200.ops import arena, gemm, mixer_ops
 from paged_kv_serving_b200.parts.base import CacheBinding, GroupView, IntArena, StepContext
 
 __all__ = ["CacheStorage", "ModelRunner", "StepResult"]
@@ -136,6 +136,7 @@ class ModelRunner:
         self.num_blocks = num_blocks
         self.block_size = block_size
         self.order = model.layout.resolved_order()
+        self._readds_input = any(call.add_input for call in self.order)
         self.groups, self.state_entries = plan_groups(model.layout.cache_entries())
         self.num_state_slots = max_running_seqs if self.state_entries else 0
         self.storage = CacheStorage(self.groups, self.state_entries, num_blocks=num_blocks, block_size=block_size,
@@ -308,13 +309,22 @@ class ModelRunner:
         blocks = model.layout.blocks
         delta = None
         step_arena = arena.active()
+        model_input = None
+        if self._readds_input:
+            # a copy that lives as long as the step: the stream itself is updated in place
+            model_input = arena.empty_for_step(hidden.shape, hidden.dtype, hidden.device)
+            model_input.copy_(hidden)
         for i, (call, binding) in enumerate(zip(self.order, self.bindings)):
             if step_arena is not None:
                 step_arena.next_layer()
+            if call.add_input:
+                # (additions commute: an update still pending behind the block before is added by this block)
+                mixer_ops.residual_add(hidden, model_input)
             # the block may carry the next block's first norm in the tail of its last kernel; the
             # last block hands on its plain update (the final norm takes only the wanted rows)
             following = blocks[self.order[i + 1].layer] if i + 1 < len(self.order) else None
-            if following is not None and getattr(following, "first_norm", None) is not None:
+            if following is not None and getattr(following, "first_norm", None) is not None \
+                    and not self.order[i + 1].add_input:
                 delta = blocks[call.layer].forward(hidden, delta, ctx, binding, next_norm=following.first_norm)
             else:
                 delta = blocks[call.layer].forward(hidden, delta, ctx, binding)

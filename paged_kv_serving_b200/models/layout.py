@@ -22,6 +22,9 @@ class LayerCall:
     #: ``(name, cache entry number)`` of the call's further states (``Part.state_requests``);
     #: ``resolved_order`` fills it in, a fresh entry per call and name.
     extra: tuple = ()
+    #: The model's input (the embedding part's output for the step's tokens) is added to the
+    #: stream once more right before this call: the start of a repeated pass over a span of layers.
+    add_input: bool = False
 
 
 @dataclass(slots=True)
@@ -108,7 +111,7 @@ class ModelLayout:
             if not 0 <= call.layer < len(self.blocks):
                 raise ValueError(f"layer call names layer {call.layer}, the model has {len(self.blocks)}")
             if call.cache is None and self.blocks[call.layer].cache_request() is not None:
-                call = LayerCall(call.layer, next_free, call.write)
+                call = LayerCall(call.layer, next_free, call.write, add_input=call.add_input)
                 next_free += 1
             out.append(call)
         # the further states of every call come after all primary entries, one entry per call and name
@@ -116,7 +119,7 @@ class ModelLayout:
             names = sorted(self.blocks[call.layer].state_requests())
             if names and not call.extra:
                 out[i] = LayerCall(call.layer, call.cache, call.write,
-                                   tuple((name, next_free + k) for k, name in enumerate(names)))
+                                   tuple((name, next_free + k) for k, name in enumerate(names)), call.add_input)
                 next_free += len(names)
         return out
 

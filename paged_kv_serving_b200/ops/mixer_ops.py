@@ -1,5 +1,6 @@
 """Bindings of the kernels in ``csrc/pointwise.cu``, ``csrc/conv_state.cu``, ``csrc/mlstm.cu``,
-``csrc/selective_scan.cu``, ``csrc/latent_attention.cu`` and ``csrc/attention_sink.cu``: what mixers
+``csrc/selective_scan.cu``, ``csrc/latent_attention.cu``, ``csrc/attention_sink.cu``, ``csrc/layernorm.cu`` and
+``csrc/lightning.cu``: what mixers
 with a state of their own, a cached latent, a window that keeps the first tokens, routed experts
 and per-token side inputs need beside the kernels bound in ``ops/__init__.py``.
 The same conventions hold: CUDA tensors only, launches on torch's current stream, a refused
@@ -19,7 +20,8 @@ from paged_kv_serving_b200.ops.arena import empty as _empty
 __all__ = ["ACTIVATIONS", "act_times_table", "bias_act", "conv_residual", "expert_act", "expert_gated_act", "norm_residual", "latent_attention",
            "latent_attention_mma", "latent_mma_rows_per_block", "latent_mma_supports", "latent_prepare",
            "latent_rows_per_block", "mlstm", "residual_add", "route_top", "token_side", "attention_sink",
-           "attention_sink_mma", "attention_sink_mma_rows", "attention_sink_mma_supports", "attention_sink_rows_per_block", "qkv_prepare", "selective_scan"]
+           "attention_sink_mma", "attention_sink_mma_rows", "attention_sink_mma_supports", "attention_sink_rows_per_block", "qkv_prepare", "selective_scan",
+           "layer_norm_step", "lightning", "softcap", "token_shift"]
 
 #: activation names of ``bias_act`` / ``act_times_table`` / ``expert_act``
 ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "relu_squared": 3, "sigmoid": 4, "silu": 5}
@@ -236,11 +238,13 @@ def latent_prepare(fused: torch.Tensor, q_off: int, q_rank: int, kv_off: int, ra
                    q_weight: torch.Tensor, kv_weight: torch.Tensor, freq: torch.Tensor, eps: float, positions: torch.Tensor,
                    slots: torch.Tensor | None, pool: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
     """From the fused down-projections ``fused`` (float32 ``[tokens, ld]``): the RMS-normalised
-    query latent ``[tokens, q_rank]`` (returned, in the pool's type), and the cache row
+    query latent ``[tokens, q_rank]`` (returned, in the pool's type; ``q_rank`` 0: there is none), and the cache row
     ``[normalised latent | rotated key part]`` written at ``slots`` (int32 per token, negative or
     ``None``: nothing is written) of ``pool [pages, 1, page_size, rank + rot]``."""
     _need(fused, torch.float32, "fused"); _need(pool, None, "pool"); _need(freq, torch.float32, "freq")
-    _need(q_weight, torch.float32, "q_weight"); _need(kv_weight, torch.float32, "kv_weight")
+    _need(kv_weight, torch.float32, "kv_weight")
+    if q_rank:
+        _need(q_weight, torch.float32, "q_weight")
     tokens, ld = fused.shape
     if pool.shape[-1] != rank + rot:
         raise ValueError("the pool's rows must hold rank + rot values")
@@ -421,11 +425,13 @@ def qkv_prepare(qkv: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor |
                 eps: float, unit_norm: bool, k_pool: torch.Tensor, v_pool: torch.Tensor, slots: torch.Tensor | None,
                 n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int, status: torch.Tensor,
                 v_other: torch.Tensor | None = None, blend: torch.Tensor | None = None,
-                keep_values: torch.Tensor | None = None) -> None:
+                keep_values: torch.Tensor | None = None, q_weight: torch.Tensor | None = None,
+                k_weight: torch.Tensor | None = None) -> None:
     """In ``qkv [tokens, >= H dim + G dim + G vdim]`` (columns ``[Q | K | V]``): rotate the first
     ``rot_dims`` coordinates of every query and key head (``freq [rot_dims / 2]`` float32 angular
     frequencies, cos and sin times ``rot_factor``), divide those heads by their root mean square
-    (``unit_norm``), write the queries back in place and the keys into ``k_pool [pages, G,
+    (``unit_norm``) and multiply them by ``q_weight`` / ``k_weight`` (float32 ``[dim]``, the same for every
+    head; ``None``: no factor), write the queries back in place and the keys into ``k_pool [pages, G,
     page_size, dim]`` at ``slots``; blend the values with ``v_other [tokens, G vdim]`` (weight
     ``blend``, a float32 tensor of one element: ``(1 - blend) v + blend v_other``) and write them
     into ``v_pool [pages, G, page_size, vdim]``. ``keep_values [tokens, G vdim]`` (type of ``qkv``)
@@ -451,11 +457,17 @@ def qkv_prepare(qkv: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor |
         if kept.shape != (tokens, n_kv * vdim):
             raise ValueError("keep_values must be [tokens, G * vdim]")
     pool_slots = k_pool.numel() // (n_kv * dim)
+    for name, t in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if t is not None:
+            _need(t, torch.float32, name)
+            if t.numel() != dim:
+                raise ValueError(f"{name} needs one element per coordinate of a head")
     fn = _fn("attention_sink", "pkv_qkv_prepare",
-             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p,
-              c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p, c_int,
+              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int,
+              c_void_p, c_void_p])
     _check(fn(_ptr(qkv), dtype_code(qkv.dtype), ld, _ptr(positions), _ptr(freq), int(rot_dims), float(rot_factor), float(eps),
-              int(bool(unit_norm)), _ptr(v_other), ld_other, _ptr(blend), _ptr(kept), _ptr(k_pool), _ptr(v_pool),
+              int(bool(unit_norm)), _ptr(q_weight), _ptr(k_weight), _ptr(v_other), ld_other, _ptr(blend), _ptr(kept), _ptr(k_pool), _ptr(v_pool),
               dtype_code(k_pool.dtype), _ptr(slots), pool_slots, tokens, n_heads, n_kv, dim, vdim, page_size, _ptr(status),
               _stream()), "qkv_prepare")
 
@@ -469,10 +481,13 @@ def attention_sink_rows_per_block() -> int:
 def attention_sink(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
                    seq_starts: torch.Tensor, first_pos: torch.Tensor, work_seq: torch.Tensor, work_row0: torch.Tensor,
                    n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int, window: int, keep_first: int, scale: float,
-                   softcap: float, status: torch.Tensor) -> torch.Tensor:
+                   softcap: float, status: torch.Tensor, head_scale: torch.Tensor | None = None,
+                   distance_bias: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
     """Paged causal attention in float32 arithmetic: scores ``q.k * scale``, capped as ``softcap *
     tanh(score / softcap)`` (0: no cap); query position ``i`` sees key ``j <= i`` when ``i - j <
-    window`` or ``j < keep_first`` (``window`` 0: every earlier key). Query head ``h`` of token
+    window`` or ``j < keep_first`` (``window`` 0: every earlier key). ``head_scale`` (float32 ``[H]``)
+    multiplies the score of its head before the cap; ``distance_bias = (a, b)`` (float32 ``[H]`` each)
+    takes ``a[h] * log(1 + b[h] * (i - j))`` off it after the cap. Query head ``h`` of token
     ``t`` is ``q[t, h * dim : (h + 1) * dim]`` (``q`` may have further columns). Returns ``[tokens, H
     * vdim]`` in the type of ``q``. The work list is in blocks of ``attention_sink_rows_per_block()``
     rows per (entry, key/value head)."""
@@ -485,14 +500,27 @@ def attention_sink(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
         raise ValueError("q is narrower than its heads")
     out = _empty((tokens, n_heads * vdim), q.dtype, q.device)
     num_pages = k_pool.numel() // (n_kv * page_size * dim)
+    bias_a, bias_b = _per_head(head_scale, distance_bias, n_heads)
     fn = _fn("attention_sink", "pkv_attention_sink",
              [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p])
+              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p,
+              c_int, c_void_p, c_void_p])
     _check(fn(_ptr(q), q.shape[1], _ptr(out), dtype_code(q.dtype), _ptr(k_pool), _ptr(v_pool), dtype_code(k_pool.dtype),
               _ptr(block_table), block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), _ptr(work_row0),
               work_seq.numel(), n_heads, n_kv, dim, vdim, page_size, int(window), int(keep_first), float(scale), float(softcap),
-              num_pages, _ptr(status), _stream()), "attention_sink")
+              _ptr(head_scale), _ptr(bias_a), _ptr(bias_b), num_pages, _ptr(status), _stream()), "attention_sink")
     return out
+
+
+def _per_head(head_scale: torch.Tensor | None, distance_bias, n_heads: int):
+    """Checks the per-head vectors of the two attention kernels; returns the bias pair (or two ``None``)."""
+    bias_a, bias_b = distance_bias if distance_bias is not None else (None, None)
+    for name, t in (("head_scale", head_scale), ("distance_bias[0]", bias_a), ("distance_bias[1]", bias_b)):
+        if t is not None:
+            _need(t, torch.float32, name)
+            if t.numel() != n_heads:
+                raise ValueError(f"{name} needs one element per query head")
+    return bias_a, bias_b
 
 
 def attention_sink_mma_supports(dim: int, vdim: int, q_row_stride: int) -> bool:
@@ -511,7 +539,8 @@ def attention_sink_mma_rows() -> int:
 def attention_sink_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
                        seq_starts: torch.Tensor, first_pos: torch.Tensor, work_seq: torch.Tensor, work_q0: torch.Tensor,
                        n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int, window: int, keep_first: int, scale: float,
-                       softcap: float, status: torch.Tensor, num_splits: int = 1) -> torch.Tensor:
+                       softcap: float, status: torch.Tensor, num_splits: int = 1, head_scale: torch.Tensor | None = None,
+                       distance_bias: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
     """``attention_sink`` on the tensor cores (``mma.sync``, bfloat16 operands, float32 scores and
     accumulators) for head sizes that are multiples of 16. The rows of an (entry, key/value head)
     are (token, head in group) pairs, ``row = token * (H / G) + head in group``; the work list is in
@@ -532,14 +561,111 @@ def attention_sink_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
     if num_splits > 1:
         part_o = _empty((tokens * n_heads * num_splits, vdim), torch.float32, q.device)
         part_ml = _empty((tokens * n_heads * num_splits, 2), torch.float32, q.device)
+    bias_a, bias_b = _per_head(head_scale, distance_bias, n_heads)
     fn = _fn("attention_sink", "pkv_attention_sink_mma",
              [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p,
-              c_longlong, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+              c_int, c_void_p, c_void_p, c_longlong, c_void_p])
     _check(fn(_ptr(q), q.shape[1], _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
               _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), _ptr(work_q0), work_seq.numel(), n_heads, n_kv, dim, vdim,
-              page_size, int(window), int(keep_first), float(scale), float(softcap), num_pages, _ptr(status), int(num_splits),
+              page_size, int(window), int(keep_first), float(scale), float(softcap), _ptr(head_scale), _ptr(bias_a), _ptr(bias_b),
+              num_pages, _ptr(status), int(num_splits),
               _ptr(part_o), _ptr(part_ml), tokens, _stream()), "attention_sink_mma")
     if num_splits > 1:
         ops.LAUNCHES["count"] += 1
     return out
+
+
+def layer_norm_step(hidden: torch.Tensor, update: torch.Tensor | None = None, post: tuple | None = None, mult: float = 1.0,
+                    addend: torch.Tensor | None = None, pre: tuple | None = None, out_dtype: torch.dtype | None = None,
+                    rows: torch.Tensor | None = None, eps: float = 1e-5) -> torch.Tensor | None:
+    """What happens to a float32 stream between two sublayers of a block whose norms are layer
+    norms with weight and bias, in one kernel and float32 arithmetic: ``hidden += mult *
+    layer_norm(update; post)`` (with ``update``; ``post = (weight, bias)``), ``hidden += addend``
+    (with ``addend``, float32 like the stream), and, with ``pre = (weight, bias)``, the layer norm
+    of the updated stream in ``out_dtype`` (returned). With ``rows`` (int32 indices) only those
+    rows are worked on, the stream itself stays as it is and the result has one row per index."""
+    _need(hidden, torch.float32, "hidden")
+    n, width = hidden.shape
+    post_w = post_b = pre_w = pre_b = None
+    if update is not None:
+        _need(update, None, "update")
+        if update.shape != hidden.shape or post is None:
+            raise ValueError("update must have the stream's shape and come with its norm's weight and bias")
+        post_w, post_b = post
+        _need(post_w, torch.float32, "post weight"); _need(post_b, torch.float32, "post bias")
+        if post_w.numel() != width or post_b.numel() != width:
+            raise ValueError("the norm's weight and bias do not fit the stream's width")
+    if addend is not None:
+        _need(addend, torch.float32, "addend")
+        if addend.shape != hidden.shape:
+            raise ValueError("addend and hidden differ in shape")
+    n_rows = n
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        n_rows = rows.numel()
+    out = None
+    if pre is not None:
+        pre_w, pre_b = pre
+        _need(pre_w, torch.float32, "pre weight"); _need(pre_b, torch.float32, "pre bias")
+        if pre_w.numel() != width or pre_b.numel() != width:
+            raise ValueError("the norm's weight and bias do not fit the stream's width")
+        out = _empty((n_rows, width), out_dtype or torch.float32, hidden.device)
+    fn = _fn("layernorm", "pkv_layer_norm_step",
+             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+              c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(hidden), _ptr(update), dtype_code(update.dtype) if update is not None else 0, _ptr(post_w), _ptr(post_b),
+              float(mult), _ptr(addend), _ptr(pre_w), _ptr(pre_b), _ptr(out), dtype_code(out.dtype) if out is not None else 0,
+              _ptr(rows), n_rows, width, float(eps), _stream()), "layer_norm_step")
+    return out
+
+
+def token_shift(h: torch.Tensor, mix: torch.Tensor, state: torch.Tensor, token_seq: torch.Tensor, seq_starts: torch.Tensor,
+                state_slots: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``h[t] + (h[t - 1] - h[t]) * mix`` for a ragged batch: ``h`` float32 ``[tokens, width]``, ``mix``
+    float32 ``[width]``; the row before an entry's first token is the request's row of ``state``
+    (float32 ``[slots, width]``), which is then set to the entry's last row of ``h``."""
+    _need(h, torch.float32, "h"); _need(mix, torch.float32, "mix"); _need(state, torch.float32, "state")
+    tokens, width = h.shape
+    if mix.numel() != width or state.dim() != 2 or state.shape[1] != width:
+        raise ValueError("token_shift: sizes do not fit")
+    out = _empty((tokens, width), out_dtype, h.device)
+    fn = _fn("layernorm", "pkv_token_shift",
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(h), _ptr(mix), _ptr(state), _ptr(token_seq), _ptr(seq_starts), _ptr(state_slots), _ptr(out),
+              dtype_code(out_dtype), tokens, seq_starts.numel() - 1, width, _stream()), "token_shift")
+    ops.LAUNCHES["count"] += 1
+    return out
+
+
+def lightning(proj: torch.Tensor, offsets: dict[str, int], decay: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+              state: torch.Tensor, seq_starts: torch.Tensor, state_slots: torch.Tensor, heads: int, dim: int, vdim: int,
+              out_dtype: torch.dtype) -> torch.Tensor:
+    """Linear attention with a fixed decay per head over a ragged batch. ``proj`` float32 ``[tokens,
+    ld]`` holds the projections before their SiLU, q and k ``[heads, dim]``, v and the gate ``[heads,
+    vdim]`` at ``offsets`` ("q", "k", "v", "g"); ``decay`` float32 ``[heads]``; ``state`` float32
+    ``[slots, heads, vdim, dim]`` is read and brought up to date. Returns the heads' outputs after
+    their joint RMS norm, its weight and the sigmoid gate, ``[tokens, heads * vdim]``."""
+    _need(proj, torch.float32, "proj"); _need(decay, torch.float32, "decay"); _need(norm_weight, torch.float32, "norm_weight")
+    _need(state, torch.float32, "state")
+    tokens, ld = proj.shape
+    if state.shape[1:] != (heads, vdim, dim) or decay.numel() != heads or norm_weight.numel() != heads * vdim:
+        raise ValueError("lightning: sizes do not fit")
+    scratch = _empty((tokens, heads * vdim), torch.float32, proj.device)
+    out = _empty((tokens, heads * vdim), out_dtype, proj.device)
+    fn = _fn("lightning", "pkv_lightning",
+             [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(proj), ld, offsets["q"], offsets["k"], offsets["v"], offsets["g"], _ptr(decay), _ptr(norm_weight), float(eps),
+              _ptr(state), _ptr(seq_starts), _ptr(state_slots), _ptr(scratch), _ptr(out), dtype_code(out_dtype), tokens,
+              seq_starts.numel() - 1, heads, dim, vdim, _stream()), "lightning")
+    ops.LAUNCHES["count"] += 1
+    return out
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """``cap * tanh(x / cap)`` in place on a float32 tensor (returned)."""
+    _need(x, torch.float32, "x")
+    fn = _fn("pointwise", "pkv_softcap", [c_void_p, c_longlong, c_float, c_void_p])
+    _check(fn(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
+    return x

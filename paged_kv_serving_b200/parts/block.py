@@ -8,7 +8,7 @@ from paged_kv_serving_b200.config.registry import register_part
 from paged_kv_serving_b200.ops import gemm
 from paged_kv_serving_b200.parts.base import Block, CacheBinding, Normed, Part, StepContext
 
-__all__ = ["ConvSideBlock", "PostNormBlock", "PreNormBlock"]
+__all__ = ["ConvSideBlock", "PostNormBlock", "PreNormBlock", "SandwichBlock"]
 
 
 @register_part("block", "prenorm_residual")
@@ -228,3 +228,92 @@ class PostNormBlock(Block):
         if wants_copy:
             return Normed(hidden if x is None else x, next_norm)
         return None
+
+
+@register_part("block", "sandwich_layernorm")
+class SandwichBlock(Block):
+    """Residual arrangement with a layer norm in front of and behind each sublayer and a factor on
+    every update: ``x += m * norm1b(mixer(shift(norm1(x))))``, then (with a feed-forward) ``x += m *
+    norm2b(feed_forward(norm2(x)))``. ``input_shift`` (a ``TokenShift``, optional) blends the
+    mixer's input with that of the token before it.
+
+    The norms are ``LayerNorm`` parts; the norm behind a sublayer, the residual add and the norm
+    in front of the next sublayer are one kernel (``ops.mixer_ops.layer_norm_step``), also across
+    the border to a following block of this kind: its ``first_norm`` is applied in the tail of
+    this block's last step and handed on as a ``Normed`` (in that norm's ``rows_dtype``: float32
+    when the block shifts its input, since the shift reads float32 rows). The block adds its updates itself, so nothing is ever pending
+    behind it.
+    """
+
+    def __init__(self, mixer_norm: Part, mixer: Part, mixer_out_norm: Part, ff_norm: Part | None = None,
+                 feed_forward: Part | None = None, ff_out_norm: Part | None = None, residual_mult: float = 1.0,
+                 input_shift: Part | None = None) -> None:
+        if (ff_norm is None) != (feed_forward is None) or (ff_out_norm is None) != (feed_forward is None):
+            raise ValueError("a feed-forward and its two norms go together")
+        self.mixer_norm, self.mixer, self.mixer_out_norm = mixer_norm, mixer, mixer_out_norm
+        self.ff_norm, self.feed_forward, self.ff_out_norm = ff_norm, feed_forward, ff_out_norm
+        self.residual_mult, self.input_shift = float(residual_mult), input_shift
+        if input_shift is not None and mixer_norm.rows_dtype != torch.float32:
+            raise ValueError("the norm in front of a shifted mixer input hands out float32 rows")
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(child.graph_safe for child in self.sub_parts().values())
+
+    def sub_parts(self) -> dict[str, Part]:
+        parts = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "mixer_out_norm": self.mixer_out_norm,
+                 "ff_norm": self.ff_norm, "feed_forward": self.feed_forward, "ff_out_norm": self.ff_out_norm,
+                 "input_shift": self.input_shift}
+        return {name: part for name, part in parts.items() if part is not None}
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def state_requests(self):
+        requests = {}
+        for child in self.sub_parts().values():
+            for name, request in child.state_requests().items():
+                if name in requests:
+                    raise ValueError(f"two parts of one block ask for a state named {name!r}")
+                requests[name] = request
+        return requests
+
+    def plan_step(self, ctx: StepContext, binding: CacheBinding | None) -> None:
+        for child in self.sub_parts().values():
+            if type(child).plan_step is not Part.plan_step:
+                child.plan_step(ctx, binding)
+
+    @property
+    def first_norm(self) -> Part:
+        return self.mixer_norm
+
+    def forward(self, hidden: torch.Tensor, pending: "torch.Tensor | Normed | None", ctx: StepContext,
+                binding: CacheBinding | None, next_norm: Part | None = None) -> "Normed | None":
+        from paged_kv_serving_b200.ops import mixer_ops
+        from paged_kv_serving_b200.parts.norms import LayerNorm
+
+        eps, mult = self.mixer_norm.eps, self.residual_mult
+        first_type = self.mixer_norm.rows_dtype or ctx.dtype
+        if isinstance(pending, Normed):
+            if pending.norm is not self.mixer_norm or pending.values.dtype != first_type:
+                raise ValueError("the stream was normalised for another block than the one that runs next")
+            h = pending.values
+        else:
+            if pending is not None:
+                mixer_ops.residual_add(hidden, pending)
+            h = mixer_ops.layer_norm_step(hidden, pre=self.mixer_norm.pair, out_dtype=first_type, eps=eps)
+        if self.input_shift is not None:
+            h = self.input_shift.forward(h, ctx, binding)
+        update = self.mixer.forward(h, ctx, binding)
+        carried = next_norm if isinstance(next_norm, LayerNorm) else None
+        carried_type = (carried.rows_dtype or ctx.dtype) if carried is not None else None
+        if self.feed_forward is not None:
+            h = mixer_ops.layer_norm_step(hidden, update, self.mixer_out_norm.pair, mult, pre=self.ff_norm.pair,
+                                          out_dtype=ctx.dtype, eps=eps)
+            update = self.feed_forward.forward(h, ctx)
+            last = self.ff_out_norm
+        else:
+            last = self.mixer_out_norm
+        values = mixer_ops.layer_norm_step(hidden, update, last.pair, mult, pre=carried.pair if carried is not None else None,
+                                           out_dtype=carried_type, eps=eps)
+        return Normed(values, carried) if carried is not None else None

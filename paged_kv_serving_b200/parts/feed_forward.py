@@ -9,7 +9,7 @@ from paged_kv_serving_b200.config.registry import register_part
 from paged_kv_serving_b200.ops import gemm
 from paged_kv_serving_b200.parts.base import ParamSpec, Part, StepContext
 
-__all__ = ["BiasedDense", "GatedRoutedExperts", "RoutedExperts", "SwiGLU"]
+__all__ = ["BiasedDense", "Dense", "GatedRoutedExperts", "RoutedExperts", "SwiGLU"]
 
 
 @register_part("feed_forward", "swiglu")
@@ -100,6 +100,31 @@ class BiasedDense(Part):
         inner = mixer_ops.bias_act(gemm.linear(x, self.up), self.up_b, self.activation)
         out = gemm.linear(inner, self.down)
         return mixer_ops.bias_act(out, self.down_b, "none") if add_bias else out
+
+
+@register_part("feed_forward", "dense")
+class Dense(Part):
+    """``W_down act(W_up x)`` without biases and without a gate (``act`` the square of relu unless
+    given); weights ``[out, in]``. The result is float32: what a norm on the sublayer's output reads."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, inner: int, activation: str = "relu_squared") -> None:
+        self.width, self.inner, self.activation = int(width), int(inner), activation
+        self.up: torch.Tensor | None = None
+        self.down: torch.Tensor | None = None
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        return {"up": ParamSpec((self.inner, self.width)), "down": ParamSpec((self.width, self.inner))}
+
+    def load(self, params: dict[str, torch.Tensor]) -> None:
+        self.up, self.down = params["up"].contiguous(), params["down"].contiguous()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        from paged_kv_serving_b200.ops import mixer_ops
+
+        inner = mixer_ops.bias_act(gemm.linear(x, self.up, chain=True), None, self.activation)
+        return gemm.linear(inner, self.down, out_dtype=torch.float32, few_rows_f32=True, chain=True)
 
 
 @register_part("feed_forward", "routed_experts")

@@ -44,15 +44,18 @@ class LinearHead(Part):
     """``logits = normed @ weight^T`` in float32, ``weight [vocab, width]``; with ``tied`` the
     weight is that embedding part's table (reference: src/paged_kv_serving/engine/model.py:261-264,
     where the head is always tied). ``forward(normed, ctx)`` gets the rows the final norm left
-    (only the wanted ones). A head with a scale, a soft cap or several outputs is another part
-    with the same ``forward``."""
+    (only the wanted ones). With ``softcap`` ``c > 0`` the logits become ``c * tanh(logits / c)``. A head
+    with a scale or several outputs is another part with the same ``forward``."""
 
     graph_safe = True
 
-    def __init__(self, vocab_size: int, width: int, tied: TokenEmbedding | None = None) -> None:
+    def __init__(self, vocab_size: int, width: int, tied: TokenEmbedding | None = None, softcap: float = 0.0) -> None:
+        if softcap < 0:
+            raise ValueError("softcap must be >= 0")
         self.vocab_size = int(vocab_size)
         self.width = int(width)
         self.tied = tied
+        self.softcap = float(softcap)
         self._weight: torch.Tensor | None = None
 
     def param_specs(self) -> dict[str, ParamSpec]:
@@ -67,4 +70,9 @@ class LinearHead(Part):
         return self.tied.table if self.tied is not None else self._weight
 
     def forward(self, normed: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        return gemm.linear(normed, self.weight, out_dtype=torch.float32, chain=True)
+        logits = gemm.linear(normed, self.weight, out_dtype=torch.float32, chain=True)
+        if self.softcap > 0.0:
+            from paged_kv_serving_b200.ops import mixer_ops
+
+            mixer_ops.softcap(logits, self.softcap)
+        return logits

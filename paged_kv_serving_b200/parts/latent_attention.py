@@ -19,16 +19,22 @@ def _round_up(value: int, multiple: int) -> int:
 
 @register_part("mixer", "latent_attention")
 class LatentAttention(Part):
-    """Causal softmax attention with low-rank queries, keys and values and an output gate.
+    """Causal softmax attention with low-rank keys and values, optionally low-rank queries and an
+    output gate.
 
-    With ``h`` the input: ``c_q = rmsnorm(W_dq h) * dq_norm`` and ``q = W_uq c_q``, laid out head
+    With ``h`` the input: ``c_q = rmsnorm(W_dq h) * dq_norm`` and ``q = W_uq c_q`` (with ``q_rank``
+    0: ``q = W_q h``, one matrix named ``q``), laid out head
     by head as ``[dim unrotated | rot_dim rotated]``. ``W_dkv h`` gives ``kv_rank`` numbers whose
     RMS norm (times ``dkv_norm``) is the latent ``c``, and ``rot_dim`` more that form one rotated
     key part shared by all heads. Head ``a`` has keys ``W_uk[a] c`` and values ``W_uv[a] c``; the
     score is ``(q_unrotated . k_unrotated + q_rotated . k_rotated) * scale``; the head's result is
-    multiplied by ``sigmoid(W_g h)[a]`` and the heads go through ``W_o``. Rotation acts on the
-    first ``rot_dims`` coordinates of the rotated parts (coordinate ``i`` pairs with
-    ``i + rot_dims / 2``) with angle ``position * base^(-2i / rot_dims)``.
+    multiplied by ``sigmoid(W_g h)[a]`` (with ``gate``) and the heads go through ``W_o``. Rotation acts on the
+    first ``rot_dims`` coordinates of the rotated parts with angle ``position * base^(-2i /
+    rot_dims)`` for pair ``i``: coordinate ``i`` pairs with ``i + rot_dims / 2`` (``pairing="halves"``) or
+    coordinate ``2i`` with ``2i + 1`` (``pairing="interleaved"``). The kernels rotate halves; for the
+    interleaved pairing the rows of the query and key projections that produce the rotated
+    coordinates are reordered at load (even ones first, then odd ones), which changes no score
+    because queries and keys are reordered alike and only their dot product is used.
 
     Only ``[c | rotated key part]`` is cached, ``kv_rank + rot_dim`` numbers a position for all
     heads (a page group without values). The kernels use the absorbed form: the unrotated query of
@@ -47,9 +53,13 @@ class LatentAttention(Part):
     USE_TENSOR_CORES = True
 
     def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int, kv_rank: int, scale: float,
-                 rot_base: float, rot_dims: int, eps: float, window: int | None = None) -> None:
+                 rot_base: float, rot_dims: int, eps: float, window: int | None = None, gate: bool = True,
+                 pairing: str = "halves") -> None:
         if rot_dims % 2 or rot_dims > rot_dim:
             raise ValueError("the rotated coordinates must be an even number within the rotated part")
+        if pairing not in ("halves", "interleaved"):
+            raise ValueError("pairing is 'halves' or 'interleaved'")
+        self.gate, self.pairing = bool(gate), pairing
         if kv_rank > 512:
             raise ValueError("the latent attention kernel takes a latent of up to 512 numbers")
         self.width, self.heads, self.dim, self.rot_dim, self.vdim = int(width), int(heads), int(dim), int(rot_dim), int(vdim)
@@ -58,7 +68,7 @@ class LatentAttention(Part):
         # columns of the fused down-projection: [query latent | key/value latent, key part | gate], padded
         self.q_off, self.kv_off = 0, self.q_rank
         self.g_off = self.q_rank + self.kv_rank + self.rot_dim
-        self.fused_rows = _round_up(self.g_off + self.heads, 8)
+        self.fused_rows = _round_up(self.g_off + (self.heads if self.gate else 0), 8)
         half = self.rot_dims // 2
         self._freq_host = np.asarray([self.rot_base ** (-2.0 * i / self.rot_dims) for i in range(half)] or [0.0],
                                      dtype=np.float64).astype(np.float32)
@@ -67,27 +77,47 @@ class LatentAttention(Part):
 
     def param_specs(self) -> dict[str, ParamSpec]:
         head = self.dim + self.rot_dim
-        return {
-            "dq": ParamSpec((self.q_rank, self.width)), "dq_norm": ParamSpec((self.q_rank,), "vector"),
-            "uq": ParamSpec((self.heads * head, self.q_rank)),
+        specs = {
             "dkv": ParamSpec((self.kv_rank + self.rot_dim, self.width)), "dkv_norm": ParamSpec((self.kv_rank,), "vector"),
             "uk": ParamSpec((self.heads * self.dim, self.kv_rank)), "uv": ParamSpec((self.heads * self.vdim, self.kv_rank)),
-            "g": ParamSpec((self.heads, self.width)), "o": ParamSpec((self.width, self.heads * self.vdim)),
+            "o": ParamSpec((self.width, self.heads * self.vdim)),
         }
+        if self.q_rank:
+            specs.update({"dq": ParamSpec((self.q_rank, self.width)), "dq_norm": ParamSpec((self.q_rank,), "vector"),
+                          "uq": ParamSpec((self.heads * head, self.q_rank))})
+        else:
+            specs["q"] = ParamSpec((self.heads * head, self.width))
+        if self.gate:
+            specs["g"] = ParamSpec((self.heads, self.width))
+        return specs
+
+    def _halves_order(self, rows: torch.Tensor, start: int) -> torch.Tensor:
+        """``rows`` with the ``rot_dims`` rows from ``start`` on reordered from interleaved pairs to halves."""
+        if self.pairing != "interleaved" or not self.rot_dims:
+            return rows
+        order = torch.arange(rows.shape[0], device=rows.device)
+        turned = torch.cat([torch.arange(0, self.rot_dims, 2), torch.arange(1, self.rot_dims, 2)]).to(rows.device)
+        order[start:start + self.rot_dims] = start + turned
+        return rows[order]
 
     def load(self, params: dict[str, torch.Tensor]) -> None:
-        dq = params["dq"]
-        fused = torch.zeros((self.fused_rows, self.width), dtype=dq.dtype, device=dq.device)
-        fused[:self.q_rank] = dq
-        fused[self.kv_off:self.g_off] = params["dkv"]
-        fused[self.g_off:self.g_off + self.heads] = params["g"]
+        head = self.dim + self.rot_dim
+        dkv = self._halves_order(params["dkv"], self.kv_rank)
+        fused = torch.zeros((self.fused_rows, self.width), dtype=dkv.dtype, device=dkv.device)
+        if self.q_rank:
+            fused[:self.q_rank] = params["dq"]
+        fused[self.kv_off:self.g_off] = dkv
+        if self.gate:
+            fused[self.g_off:self.g_off + self.heads] = params["g"]
         self.down = fused                                                     # [fused_rows, width]
-        self.uq = params["uq"].contiguous()
+        up = params["uq"] if self.q_rank else params["q"]
+        up = up.view(self.heads, head, up.shape[1])
+        self.uq = torch.stack([self._halves_order(up[a], self.dim) for a in range(self.heads)]).view(self.heads * head, -1).contiguous()
         self.uk = params["uk"].view(self.heads, self.dim, self.kv_rank).contiguous()        # q_lat = q_unrot @ uk[a]
         self.uv_t = params["uv"].view(self.heads, self.vdim, self.kv_rank).transpose(1, 2).contiguous()   # [a, rank, vdim]
         self.o = params["o"].contiguous()
-        self.dq_norm, self.dkv_norm = params["dq_norm"], params["dkv_norm"]
-        self.freq = torch.from_numpy(self._freq_host).to(dq.device)
+        self.dq_norm, self.dkv_norm = params.get("dq_norm"), params["dkv_norm"]
+        self.freq = torch.from_numpy(self._freq_host).to(dkv.device)
 
     def cache_request(self) -> PagedKVRequest:
         return PagedKVRequest(1, self.kv_rank + self.rot_dim, self.window, values=False)
@@ -141,12 +171,12 @@ class LatentAttention(Part):
         c_q = mixer_ops.latent_prepare(fused, self.q_off, self.q_rank, self.kv_off, self.kv_rank, self.rot_dim, self.rot_dims,
                                        self.dq_norm, self.dkv_norm, self.freq, self.eps, ctx.ints(ctx.POSITIONS), slots, pool,
                                        ctx.status)
-        q = gemm.linear(c_q, self.uq)                                          # [tokens, heads * (dim + rot_dim)]
+        q = gemm.linear(c_q if self.q_rank else x, self.uq)                    # [tokens, heads * (dim + rot_dim)]
         q_unrotated = q.view(tokens, self.heads, head)[:, :, :self.dim].transpose(0, 1)     # [heads, tokens, dim], a view
         q_lat = torch.bmm(q_unrotated, self.uk, out_dtype=torch.float32) if q.dtype != torch.float32 \
             else torch.bmm(q_unrotated, self.uk)
         seq_name, row_name = self._work_names(ctx)
-        gate = fused[:, self.g_off:self.g_off + self.heads]
+        gate = fused[:, self.g_off:self.g_off + self.heads] if self.gate else None
         kernel = mixer_ops.latent_attention_mma if self._tensor_cores(ctx) else mixer_ops.latent_attention
         extra = {"num_splits": ctx.scratch.get(seq_name, 1)} if self._tensor_cores(ctx) else {}
         attended = kernel(

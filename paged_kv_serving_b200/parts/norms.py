@@ -9,7 +9,7 @@ from paged_kv_serving_b200.ops import gemm
 from paged_kv_serving_b200.config.registry import register_part
 from paged_kv_serving_b200.parts.base import ParamSpec, Part
 
-__all__ = ["IdentityNorm", "OffsetRMSNorm", "RMSNorm", "ScalarRMSNorm"]
+__all__ = ["IdentityNorm", "LayerNorm", "OffsetRMSNorm", "RMSNorm", "ScalarRMSNorm"]
 
 
 @register_part("norm", "rmsnorm")
@@ -99,3 +99,37 @@ class IdentityNorm(Part):
             return hidden
         out = mixer_ops.residual_add(hidden, delta, None, None if out_dtype == torch.float32 else out_dtype)
         return hidden if out is None else out
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(Part):
+    """``y = (x - mean) / sqrt(variance + eps) * weight + bias`` in float32, the variance being the
+    mean of the squared deviations from the mean. ``add_norm`` is the interface every norm has
+    (the pending update is added to the stream first); a block that wraps its sublayers in such
+    norms calls ``ops.mixer_ops.layer_norm_step`` with the weights of two of them at once.
+    ``rows_dtype`` is the type of the rows the norm hands out when a block applies it for its
+    owner (``None``: the compute type; float32 for a norm whose rows an element-wise step reads)."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, eps: float, rows_dtype: torch.dtype | None = None) -> None:
+        self.width = int(width)
+        self.eps = float(eps)
+        self.rows_dtype = rows_dtype
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        return {"weight": ParamSpec((self.width,), "vector"), "bias": ParamSpec((self.width,), "vector", init=(0.0, 0.02))}
+
+    @property
+    def pair(self) -> tuple[torch.Tensor, torch.Tensor]:
+        return self.weight, self.bias
+
+    def add_norm(self, hidden: torch.Tensor, delta: torch.Tensor | None, out_dtype: torch.dtype,
+                 rows: torch.Tensor | None = None) -> torch.Tensor:
+        from paged_kv_serving_b200.ops import mixer_ops
+
+        if delta is not None:
+            mixer_ops.residual_add(hidden, delta)
+        return mixer_ops.layer_norm_step(hidden, pre=self.pair, out_dtype=out_dtype, rows=rows, eps=self.eps)

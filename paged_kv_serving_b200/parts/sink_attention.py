@@ -28,8 +28,12 @@ class SinkWindowAttention(Part):
     * ``rotary``: a ``ScaledRotaryFrequencies`` that turns the first coordinates of every query and
       key head by the token's position (``None``: no rotation);
     * ``unit_norm``: after the rotation every query and key head is divided by its root mean square
-      (``eps`` inside the root), no weight;
-    * ``score = q . k * scale``, then, with ``softcap`` ``c > 0``, ``c * tanh(score / c)``;
+      (``eps`` inside the root); with ``norm_weights`` the result is multiplied by the tensor
+      ``q_norm`` (queries) or ``k_norm`` (keys), ``[dim]`` each and the same for every head;
+    * ``score = q . k * scale``, with ``head_temperature`` times the head's entry of the tensor ``temp``
+      ``[H]``, then, with ``softcap`` ``c > 0``, ``c * tanh(score / c)``; with ``distance_bias`` the score of
+      query position ``i`` and key position ``j`` then loses ``r1[h] * ln(1 + r2[h] * (i - j))`` (tensors
+      ``r1``, ``r2`` ``[H]``);
     * ``window`` and ``keep_first``: position ``i`` sees ``j <= i`` when ``i - j < window`` or ``j <
       keep_first`` (``window=None``: all earlier positions); kept tokens keep their own positions;
     * ``value_share``: ``"source"`` leaves this layer's values of the step's tokens in the step's
@@ -41,8 +45,8 @@ class SinkWindowAttention(Part):
     page_size, vdim]``. Angles, norms, scores, softmax and the blend are float32 arithmetic.
 
     Kernels: one for rotation, unit norm, blend and cache write (``ops.mixer_ops.qkv_prepare``);
-    for the attention itself, in bfloat16 with keys and values of one size of 64 or 128 and pages
-    of a multiple of 8 keys, the tensor-core kernels of ``PagedAttention`` (tcgen05 for runs of
+    for the attention itself, in bfloat16 with keys and values of one size of 64 or 128, pages
+    of a multiple of 8 keys and neither temperature nor distance bias, the tensor-core kernels of ``PagedAttention`` (tcgen05 for runs of
     queries, the TMA-fed split-key kernel for entries of a few rows), which take the kept first
     tokens as further tiles in front of the window's and cap the scores in their softmax; in
     bfloat16 with other head sizes that are multiples of 16 (keys and values may differ) the
@@ -57,7 +61,8 @@ class SinkWindowAttention(Part):
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
                  rotary: ScaledRotaryFrequencies | None = None, unit_norm: bool = True, eps: float = 1e-6,
                  softcap: float = 0.0, window: int | None = None, keep_first: int = 0, value_share: str | None = None,
-                 share_key: str = "sink_attention/shared_values") -> None:
+                 share_key: str = "sink_attention/shared_values", norm_weights: bool = False,
+                 head_temperature: bool = False, distance_bias: bool = False) -> None:
         if n_heads < 1 or n_kv_heads < 1 or n_heads % n_kv_heads:
             raise ValueError("n_heads must be a multiple of n_kv_heads")
         if window is not None and window < 1:
@@ -74,6 +79,10 @@ class SinkWindowAttention(Part):
         self.rotary, self.unit_norm = rotary, bool(unit_norm)
         self.window, self.keep_first = window, int(keep_first)
         self.value_share, self.share_key = value_share, share_key
+        if norm_weights and not unit_norm:
+            raise ValueError("norm weights belong to the unit norm of queries and keys")
+        self.norm_weights, self.head_temperature, self.distance_bias = bool(norm_weights), bool(head_temperature), bool(distance_bias)
+        self.q_norm = self.k_norm = self.temp = self.r1 = self.r2 = None
         self.q_cols = self.n_heads * self.dim
         self.kv_cols = self.n_kv_heads * (self.dim + self.vdim)
         self.fused_rows = _round_up(self.q_cols + self.kv_cols, 8)
@@ -90,6 +99,14 @@ class SinkWindowAttention(Part):
         }
         if self.value_share is not None:
             specs["vmix"] = ParamSpec((), "vector", init=(0.5, 0.0))
+        if self.norm_weights:
+            specs["q_norm"] = ParamSpec((self.dim,), "vector")
+            specs["k_norm"] = ParamSpec((self.dim,), "vector")
+        if self.head_temperature:
+            specs["temp"] = ParamSpec((self.n_heads,), "vector", init=(1.0, 0.2))
+        if self.distance_bias:
+            specs["r1"] = ParamSpec((self.n_heads,), "vector", init=(0.5, 0.2))
+            specs["r2"] = ParamSpec((self.n_heads,), "vector", init=(0.5, 0.2))
         return specs
 
     def load(self, params: dict[str, torch.Tensor]) -> None:
@@ -103,6 +120,8 @@ class SinkWindowAttention(Part):
         self.qkv = fused                                   # [H dim + G dim + G vdim (padded), width]
         self.o = params["o"].contiguous()
         self.blend = params["vmix"].reshape(1).contiguous() if "vmix" in params else None
+        for name in ("q_norm", "k_norm", "temp", "r1", "r2"):
+            setattr(self, name, params[name].contiguous() if name in params else None)
 
     def cache_request(self) -> PagedKVRequest:
         return PagedKVRequest(self.n_kv_heads, self.dim, self.window, value_dim=self.vdim,
@@ -135,6 +154,8 @@ class SinkWindowAttention(Part):
     def _fast(self, ctx: StepContext, page_size: int) -> bool:
         """Whether the tensor-core kernels serve this mixer in this step."""
         if not self.USE_TENSOR_CORES or ctx.dtype != torch.bfloat16 or self.dim != self.vdim:
+            return False
+        if self.head_temperature or self.distance_bias:      # those kernels know neither
             return False
         key = page_size
         if key not in self._fast_ok:
@@ -275,7 +296,9 @@ class SinkWindowAttention(Part):
             qkv, ctx.ints(ctx.POSITIONS), rotary.device_frequencies(ctx.device) if rotary else None,
             rotary.dims if rotary else 0, rotary.amplitude if rotary else 1.0, self.eps, self.unit_norm, k_pool, v_pool,
             slots, self.n_heads, self.n_kv_heads, self.dim, self.vdim, group.page_size, ctx.status,
-            v_other=other, blend=self.blend if other is not None else None, keep_values=shared)
+            v_other=other, blend=self.blend if other is not None else None, keep_values=shared,
+            q_weight=self.q_norm, k_weight=self.k_norm)
+        bias = (self.r1, self.r2) if self.distance_bias else None
         if self._fast(ctx, group.page_size):
             return gemm.linear(self._attend_fast(qkv, ctx, group, k_pool, v_pool), self.o, out_dtype=torch.float32, few_rows_f32=True)
         if self._mma(ctx):
@@ -283,12 +306,12 @@ class SinkWindowAttention(Part):
                 qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
                 ctx.ints(self._mma_names()[0]), ctx.ints(self._mma_names()[1]), self.n_heads, self.n_kv_heads,
                 self.dim, self.vdim, group.page_size, self.window or 0, self.keep_first, self.scale, self.softcap, ctx.status,
-                num_splits=self._mma_splits(ctx))
+                num_splits=self._mma_splits(ctx), head_scale=self.temp, distance_bias=bias)
             return gemm.linear(attended, self.o, out_dtype=torch.float32, few_rows_f32=True, chain=True)
         seq_name, row_name = self._work_names()
         attended = mixer_ops.attention_sink(
             qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
             ctx.ints(seq_name), ctx.ints(row_name), self.n_heads, self.n_kv_heads, self.dim, self.vdim, group.page_size,
-            self.window or 0, self.keep_first, self.scale, self.softcap, ctx.status)
+            self.window or 0, self.keep_first, self.scale, self.softcap, ctx.status, head_scale=self.temp, distance_bias=bias)
         # the float32 result of the last product goes to a norm
         return gemm.linear(attended, self.o, out_dtype=torch.float32, few_rows_f32=True, chain=True)
