@@ -1,6 +1,6 @@
 """Prefill and decode throughput of one architecture at layer sizes of a real model (random
 weights), with the time of every kernel of a step against its roofline. ``bench.py --design``
-runs it for the Revupel or the Tiburax design and, at equal sizes, for the models it is compared with.
+runs it for the Revupel, the Tiburax or the Rodelix design and, at equal sizes, for the models it is compared with.
 
 A step runs through ``ModelRunner.step``. For the kernel table one eager step is run with every
 kernel call of ``ops`` / ``ops.mixer_ops`` and every library product bracketed by CUDA events on
@@ -14,7 +14,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-__all__ = ["SIZES", "TIBURAX_SIZES", "llama_like", "measure", "revupel_config", "tiburax_config"]
+__all__ = ["RODELIX_SIZES", "SIZES", "TIBURAX_SIZES", "llama_like", "measure", "revupel_config", "rodelix_config", "tiburax_config"]
 
 #: name -> sizes of a Revupel model whose layers resemble a served model's (latent attention of
 #: the kind with a compressed cache, an mLSTM block, eight experts of which two run, a dense block)
@@ -69,6 +69,32 @@ def tiburax_config(size: str) -> dict:
             "embedding": {"scale": float(z["width"]) ** 0.5}, "layers": layers}
 
 
+#: name -> sizes of a Rodelix model at the same width and layer count: attention over a cached latent,
+#: linear attention with a decay per head (heads of 128 by 128), grouped-query attention over a
+#: window of 1,024 (heads of 128), dense feed-forwards
+RODELIX_SIZES = {
+    "1b": dict(width=2048, heads=16, kv_heads=4, dim=128, rot_dim=64, vdim=128, kv_rank=256, window=1024, l_heads=16, l_dim=128,
+               l_vdim=128, ff=8192, vocab=32000),
+    "7b": dict(width=4096, heads=32, kv_heads=8, dim=128, rot_dim=64, vdim=128, kv_rank=512, window=1024, l_heads=32, l_dim=128,
+               l_vdim=128, ff=14336, vocab=32000),
+}
+
+
+def rodelix_config(size: str) -> dict:
+    z = RODELIX_SIZES[size]
+    latent = {"type": "latent_attention", "mixer": {
+        "heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot_dim"], "vdim": z["vdim"], "kv_rank": z["kv_rank"],
+        "scale": (z["dim"] + z["rot_dim"]) ** -0.5, "rot": {"base": 10000.0, "dims": z["rot_dim"]}}}
+    window = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
+                                             "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}}}
+    decays = [1.0 - 2.0 ** (-5.0 - 3.0 * a / max(z["l_heads"] - 1, 1)) for a in range(z["l_heads"])]
+    linear = {"type": "lightning", "mixer": {"heads": z["l_heads"], "dim": z["l_dim"], "vdim": z["l_vdim"], "decay": decays}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    layers = [{**latent, "mlp": dense}, {**linear, "mlp": dense}, {**window, "mlp": dense}, {**linear, "mlp": dense}]
+    return {"architecture": "Rodelix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.7,
+            "logit_softcap": 30.0, "layers": layers}
+
+
 def llama_like(size: str) -> dict:
     """The Llama-style decoder at the same width, layer count and head count; its gated
     feed-forward has the parameter count of the dense block above."""
@@ -121,7 +147,8 @@ class _KernelTimes:
             self._wrap(ops, name, "kernel")
         for name in ("bias_act", "residual_add", "act_times_table", "route_top", "expert_act", "conv_residual", "mlstm",
                      "latent_prepare", "latent_attention", "latent_attention_mma", "norm_residual", "expert_gated_act",
-                     "qkv_prepare", "attention_sink", "attention_sink_mma", "selective_scan"):
+                     "qkv_prepare", "attention_sink", "attention_sink_mma", "selective_scan", "layer_norm_step", "token_shift",
+                     "lightning", "softcap"):
             self._wrap(mixer_ops, name, "kernel")
         self._wrap(gemm, "matmul", "product")
         self._wrap(torch, "bmm", "product")
@@ -234,6 +261,12 @@ def measure(config: dict, peaks: dict, *, prefill_tokens: int = 2048, batch: int
         moved = x.numel() * (2 * x.element_size() + 4) + out.numel() * out.element_size()
         return moved, 0.0
 
+    def lightning_cost(args, out):
+        # lightning(proj, offsets, decay, norm_weight, eps, state, starts, slots, heads, dim, vdim, out_dtype)
+        heads, dim, vdim = args[8], args[9], args[10]
+        return _bytes_of((args[0], out)) + out.numel() * 8, 4.0 * args[0].shape[0] * heads * dim * vdim
+
+    cost["lightning"] = lightning_cost
     cost.update({"attention_sink": sink_cost, "attention_sink_mma": sink_cost, "selective_scan": scan_cost})
     cost.update({"latent_attention": latent_cost, "latent_attention_mma": latent_cost,
                  "attention_prefill_tcgen05": llama_prefill_cost, "attention_prefill_bf16": llama_prefill_cost,
