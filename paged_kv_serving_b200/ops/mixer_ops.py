@@ -21,7 +21,7 @@ __all__ = ["ACTIVATIONS", "act_times_table", "bias_act", "conv_residual", "exper
            "latent_attention_mma", "latent_mma_rows_per_block", "latent_mma_supports", "latent_prepare",
            "latent_rows_per_block", "mlstm", "residual_add", "route_top", "token_side", "attention_sink",
            "attention_sink_mma", "attention_sink_mma_rows", "attention_sink_mma_supports", "attention_sink_rows_per_block", "qkv_prepare", "selective_scan",
-           "layer_norm_step", "lightning", "softcap", "token_shift"]
+           "layer_norm_step", "lightning", "lightning_chunk", "softcap", "token_shift"]
 
 #: activation names of ``bias_act`` / ``act_times_table`` / ``expert_act``
 ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "relu_squared": 3, "sigmoid": 4, "silu": 5}
@@ -638,6 +638,22 @@ def token_shift(h: torch.Tensor, mix: torch.Tensor, state: torch.Tensor, token_s
     return out
 
 
+#: tokens of one entry up to which the linear-attention kernel walks them in a row
+LIGHTNING_IN_A_ROW = 128
+#: chunk sizes of the cut form: 64 tokens, or more so that a step has about 64 chunks at most
+LIGHTNING_CHUNK, LIGHTNING_CHUNKS = 64, 64
+
+
+def lightning_chunk(tokens: int, seqs: int) -> int:
+    """Tokens per chunk for a step of ``tokens`` tokens in ``seqs`` entries (the host knows no more
+    than these two numbers when a step is captured): 0 when no entry can be longer than
+    ``LIGHTNING_IN_A_ROW``, else ``LIGHTNING_CHUNK`` or, for very long steps, a multiple of 16 that
+    keeps the working memory at about ``LIGHTNING_CHUNKS`` states per head."""
+    if tokens - (seqs - 1) <= LIGHTNING_IN_A_ROW:
+        return 0
+    return max(LIGHTNING_CHUNK, -(-tokens // (LIGHTNING_CHUNKS * 16)) * 16)
+
+
 def lightning(proj: torch.Tensor, offsets: dict[str, int], decay: torch.Tensor, norm_weight: torch.Tensor, eps: float,
               state: torch.Tensor, seq_starts: torch.Tensor, state_slots: torch.Tensor, heads: int, dim: int, vdim: int,
               out_dtype: torch.dtype) -> torch.Tensor:
@@ -645,21 +661,27 @@ def lightning(proj: torch.Tensor, offsets: dict[str, int], decay: torch.Tensor, 
     ld]`` holds the projections before their SiLU, q and k ``[heads, dim]``, v and the gate ``[heads,
     vdim]`` at ``offsets`` ("q", "k", "v", "g"); ``decay`` float32 ``[heads]``; ``state`` float32
     ``[slots, heads, vdim, dim]`` is read and brought up to date. Returns the heads' outputs after
-    their joint RMS norm, its weight and the sigmoid gate, ``[tokens, heads * vdim]``."""
+    their joint RMS norm, its weight and the sigmoid gate, ``[tokens, heads * vdim]``.
+
+    A step whose longest entry can exceed ``LIGHTNING_IN_A_ROW`` tokens is cut into chunks that run
+    side by side (``lightning_chunk``); the others walk each entry's tokens in a row, one launch."""
     _need(proj, torch.float32, "proj"); _need(decay, torch.float32, "decay"); _need(norm_weight, torch.float32, "norm_weight")
     _need(state, torch.float32, "state")
     tokens, ld = proj.shape
     if state.shape[1:] != (heads, vdim, dim) or decay.numel() != heads or norm_weight.numel() != heads * vdim:
         raise ValueError("lightning: sizes do not fit")
+    seqs = seq_starts.numel() - 1
     scratch = _empty((tokens, heads * vdim), torch.float32, proj.device)
     out = _empty((tokens, heads * vdim), out_dtype, proj.device)
+    chunk = lightning_chunk(tokens, seqs)
+    chunk_state = _empty((tokens // chunk + seqs, heads, vdim, dim), torch.float32, proj.device) if chunk else None
     fn = _fn("lightning", "pkv_lightning",
              [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
-              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(fn(_ptr(proj), ld, offsets["q"], offsets["k"], offsets["v"], offsets["g"], _ptr(decay), _ptr(norm_weight), float(eps),
               _ptr(state), _ptr(seq_starts), _ptr(state_slots), _ptr(scratch), _ptr(out), dtype_code(out_dtype), tokens,
-              seq_starts.numel() - 1, heads, dim, vdim, _stream()), "lightning")
-    ops.LAUNCHES["count"] += 1
+              seqs, heads, dim, vdim, chunk, _ptr(chunk_state) if chunk else None, _stream()), "lightning")
+    ops.LAUNCHES["count"] += 3 if chunk else 1
     return out
 
 

@@ -476,6 +476,62 @@ def test_norm_and_shift_kernels_against_the_plain_functions():
     assert torch.equal(state_dev[2].cpu(), hidden[3]) and torch.equal(state_dev[0].cpu(), hidden[10])
 
 
+def _plain_lightning_rows(proj, offsets, decay, weight, eps, state, heads, dim, vdim):
+    """Token by token in float64 on one entry's rows; ``state [heads, dim, vdim]`` is updated in place."""
+    silu = lambda z: z / (1.0 + torch.exp(-z))
+    n = proj.shape[0]
+    q = silu(proj[:, offsets["q"]:offsets["q"] + heads * dim]).view(n, heads, dim)
+    k = silu(proj[:, offsets["k"]:offsets["k"] + heads * dim]).view(n, heads, dim)
+    v = silu(proj[:, offsets["v"]:offsets["v"] + heads * vdim]).view(n, heads, vdim)
+    gate = torch.sigmoid(proj[:, offsets["g"]:offsets["g"] + heads * vdim])
+    rows = []
+    for t in range(n):
+        state.mul_(decay[:, None, None]).add_(k[t][:, :, None] * v[t][:, None, :])
+        rows.append(torch.einsum("hdv,hd->hv", state, q[t]).reshape(heads * vdim))
+    o = torch.stack(rows)
+    return o / torch.sqrt((o * o).mean(dim=1, keepdim=True) + eps) * weight * gate
+
+
+@pytest.mark.parametrize("heads,dim,vdim", [(3, 12, 20), (2, 32, 64), (1, 128, 24), (2, 130, 8), (5, 7, 3)])
+def test_linear_attention_kernel_in_a_row_and_in_chunks_over_ragged_entries(heads, dim, vdim):
+    """Entries of unequal lengths whose ends fall before, on and after chunk edges, an entry of one
+    token and an empty one, in two steps so that the second starts from states the first left; a
+    short step (every entry in a row) beside long ones (chunks side by side), all against the
+    recurrence token by token."""
+    from paged_kv_serving_b200.ops import mixer_ops
+
+    rng = torch.Generator().manual_seed(heads * 1000 + dim)
+    qk, vg = heads * dim, heads * vdim
+    offsets = {"q": 0, "k": qk, "v": 2 * qk, "g": 2 * qk + vg}
+    ld = 2 * qk + 2 * vg + 3
+    decay = torch.tensor([0.999, 0.5, 0.93, 1.0, 0.8][:heads], dtype=torch.float64)
+    weight = torch.randn((vg,), generator=rng).double()
+    slots = [4, 0, 2, 5, 1]
+    plain_states = {slot: torch.zeros((heads, dim, vdim), dtype=torch.float64) for slot in slots}
+    state = torch.zeros((6, heads, vdim, dim), dtype=torch.float32).cuda()
+    ints = lambda values: torch.tensor(values, dtype=torch.int32).cuda()
+    for lengths, cut in (([130, 1, 64, 0, 197], True), ([63, 129, 2, 5, 128], True), ([3, 1, 2, 0, 4], False),
+                         ([1000, 0, 0, 1, 0], True)):
+        assert (mixer_ops.lightning_chunk(sum(lengths), len(lengths)) > 0) == cut
+        tokens = sum(lengths)
+        proj = (torch.randn((tokens, ld), generator=rng) * 1.5).float()
+        starts = [0]
+        for n in lengths:
+            starts.append(starts[-1] + n)
+        got = mixer_ops.lightning(proj.cuda(), offsets, decay.float().cuda(), weight.float().cuda(), 1e-5, state, ints(starts),
+                                  ints(slots), heads, dim, vdim, torch.float32).cpu().double()
+        for s, slot in enumerate(slots):
+            if lengths[s] == 0:
+                continue
+            want = _plain_lightning_rows(proj[starts[s]:starts[s + 1]].double(), offsets, decay, weight, 1e-5, plain_states[slot],
+                                         heads, dim, vdim)
+            assert (got[starts[s]:starts[s + 1]] - want).abs().max() <= 2e-4 * want.abs().max(), (lengths, s)
+        for slot in slots:
+            held = state[slot].cpu().double().transpose(1, 2)
+            assert (held - plain_states[slot]).abs().max() <= 1e-5 * max(1.0, plain_states[slot].abs().max().item()), (lengths, slot)
+    assert state[3].abs().max().item() == 0.0               # a slot no entry named
+
+
 # --- rows that a single key decides ------------------------------------------------------------------
 
 
