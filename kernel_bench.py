@@ -5,7 +5,7 @@ rotates over 32 layers' worth of buffers (so that weights, keys and values come 
 a real step) and reports microseconds per launch with the achieved bandwidth or arithmetic rate.
 The sizes come from a preset of ``config/presets.py``; nothing here is used by the engine.
 
-    python kernel_bench.py [gemm] [decode-gemm] [prefill-attention] [decode-attention] [elementwise] [scan] [sink-attention]
+    python kernel_bench.py [gemm] [decode-gemm] [prefill-attention] [decode-attention] [elementwise] [scan] [sink-attention] [lightning]
 """
 
 from __future__ import annotations
@@ -226,6 +226,30 @@ def bench_scan(config, page: int) -> None:
               f"{tokens * inner * n_state / us / 1e3:6.1f} G state updates/s")
 
 
+def bench_lightning(config, page: int) -> None:
+    """Linear attention with a fixed decay per head, 16 heads of 128 by 128 (the sizes of ``bench.py --design
+    rodelix`` at width 2,048): one prompt of 2,048 tokens (chunks side by side), one of 128 (in a row), and a
+    decode step of 8 requests."""
+    from paged_kv_serving_b200.ops import mixer_ops
+
+    heads, dim, vdim = 16, 128, 128
+    qk, vg = heads * dim, heads * vdim
+    offsets = {"q": 0, "k": qk, "v": 2 * qk, "g": 2 * qk + vg}
+    decay = torch.linspace(0.96, 0.999, heads, device="cuda")
+    weight = torch.ones((vg,), device="cuda")
+    for tokens, seqs in ((2048, 1), (128, 1), (8, 8)):
+        proj = [torch.randn((tokens, 2 * qk + 2 * vg), device="cuda") for _ in range(4)]
+        state = torch.zeros((seqs, heads, vdim, dim), device="cuda")
+        starts = torch.arange(0, tokens + 1, tokens // seqs, device="cuda", dtype=torch.int32)
+        slots = torch.arange(seqs, device="cuda", dtype=torch.int32)
+        us = timed(lambda i: mixer_ops.lightning(proj[i % 4], offsets, decay, weight, 1e-5, state, starts, slots, heads, dim, vdim,
+                                                 torch.bfloat16))
+        moved = tokens * (2 * qk + 2 * vg) * 4 + tokens * vg * 2 + 2 * seqs * heads * vdim * dim * 4
+        chunk = mixer_ops.lightning_chunk(tokens, seqs)
+        print(f"lightning {tokens:5d} tokens in {seqs} sequences ({f'chunks of {chunk}' if chunk else 'in a row'}): {us:7.1f} us, "
+              f"{moved / us / 1e6:5.2f} TB/s of activations and states, {2 * tokens * heads * dim * vdim / us / 1e6:6.2f} T multiply-adds/s")
+
+
 def bench_sink_attention(config, page: int) -> None:
     """Attention over a window of 1,024 keys with 4 kept first tokens and a score cap, 16 query and 4 key/value
     heads: heads of 128 (tcgen05 for a prompt, the TMA-fed kernel for decode entries), and keys of 96 with values
@@ -294,7 +318,8 @@ def bench_sink_attention(config, page: int) -> None:
 
 def main() -> int:
     cases = {"gemm": None, "decode-gemm": None, "prefill-attention": bench_prefill_attention, "decode-attention": bench_decode_attention,
-             "elementwise": bench_elementwise, "scan": bench_scan, "sink-attention": bench_sink_attention}
+             "elementwise": bench_elementwise, "scan": bench_scan, "sink-attention": bench_sink_attention,
+             "lightning": bench_lightning}
     parser = argparse.ArgumentParser(description=__doc__.splitlines()[0])
     parser.add_argument("cases", nargs="*", choices=[*cases, []], help="which kernels to time (default: all)")
     parser.add_argument("--preset", default="llama-3-8b")
