@@ -47,8 +47,19 @@ struct FaParams {
   int pool_rows;                 // rows of the key/value maps; a row coordinate >= this reads zeros
   int keep_first;                // with a window: keys at positions below this stay visible to every later query
   float cap_log2, cap_x;         // score cap c: c * log2(e), and 2 * scale / c * log2(e); unused without a cap
+  // SHAPED, each null or float32 [n_heads]: the scaled score is multiplied by head_scale[h], then loses
+  // bias_a[h] * ln(1 + bias_b[h] * (query position - key position))
+  const float* head_scale;
+  const float* bias_a;
+  const float* bias_b;
   int* status;
 };
+
+__device__ __forceinline__ float lg2_approx(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -64,9 +75,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
 //
 // CAP: scores are capped, c * tanh(score * scale / c), before the softmax; tanh(x) = 1 - 2 / (1 + e^(2x))
 // costs two more special-function operations per score.
+// SHAPED (without CAP): a factor per head on the score and a bias that grows with the logarithm of the
+// distance, both in float32; the factor may have any sign, so the maximum is taken over the finished
+// scores, and the bias costs one lg2 per score.
 // A window may keep the first tokens of a sequence visible (keep_first): the tiles that hold them
 // are walked first, then the tiles of the window (one list of tiles; where the two meet, one range).
-template <int HD, int KT, bool WIDE, bool CAP>
+template <int HD, int KT, bool WIDE, bool CAP, bool SHAPED>
 __global__ void __launch_bounds__(FA_THREADS, KT == 64 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const FaParams p) {
@@ -259,6 +273,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
     float m_ref = -INFINITY, l = 0.0f;
     bool ok = true;
+    // SHAPED: the score in log2 units is raw * shaped_scale - shaped_a * lg2(1 + shaped_b * distance)
+    const float shaped_scale = SHAPED && p.head_scale ? p.scale_log2 * p.head_scale[head] : p.scale_log2;
+    const float shaped_a = SHAPED && p.bias_a ? p.bias_a[head] : 0.0f, shaped_b = SHAPED && p.bias_a ? p.bias_b[head] : 0.0f;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int buf = j & 1;
       const int tile_base = tile_of(j) * FA_BN;
@@ -278,7 +295,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                              (p.window > 0 && tile_base < key_hi - p.window);
       // maximum of the raw scores (the scale is positive, so it can be applied to the maximum)
       float tmax = -INFINITY;
-      if (need_mask) {
+      if (SHAPED) {
+#pragma unroll
+        for (int c = 0; c < FA_BN; ++c) {
+          const int kpos = tile_base + c;
+          const bool visible = !need_mask || (kpos <= qpos && (p.window == 0 || kpos > qpos - p.window || kpos < keep));
+          const float far = (float)max(qpos - kpos, 0);
+          const float shaped = fmaf(sc[c], shaped_scale, -shaped_a * lg2_approx(fmaf(shaped_b, far, 1.0f)));
+          sc[c] = visible ? shaped : -INFINITY;
+          tmax = fmaxf(tmax, sc[c]);
+        }
+      } else if (need_mask) {
 #pragma unroll
         for (int c = 0; c < FA_BN; ++c) {
           const int kpos = tile_base + c;
@@ -301,7 +328,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         return raw == -INFINITY ? -INFINITY : p.cap_log2 * t;
       };
       if (CAP) tmax = capped(tmax);        // the cap grows with the score: the maximum may be capped after it was found
-      else tmax *= p.scale_log2;
+      else if (!SHAPED) tmax *= p.scale_log2;
       // the reference maximum moves only when the row's maximum outgrew it by 2^8
       const bool grow = tmax > m_ref + FA_RESCALE_STEP;
       const float m_new = grow ? tmax : m_ref;
@@ -317,6 +344,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           sc[c + 1] = ex2_approx(capped(sc[c + 1]) + neg_shift);
           sc[c + 2] = ex2_approx(capped(sc[c + 2]) + neg_shift);
           sc[c + 3] = ex2_approx(capped(sc[c + 3]) + neg_shift);
+        } else if (SHAPED) {
+          sc[c] = ex2_approx(sc[c] + neg_shift);
+          sc[c + 1] = ex2_approx(sc[c + 1] + neg_shift);
+          sc[c + 2] = ex2_approx(sc[c + 2] + neg_shift);
+          sc[c + 3] = ex2_approx(sc[c + 3] + neg_shift);
         } else {
           sc[c] = ex2_approx(fmaf(sc[c], p.scale_log2, neg_shift));
           sc[c + 1] = ex2_approx(fmaf(sc[c + 1], p.scale_log2, neg_shift));
@@ -445,7 +477,7 @@ static bool pool_map(const void* base, long long rows, int hd, int box_rows, int
   return true;
 }
 
-template <int HD, int KT, bool WIDE, bool CAP>
+template <int HD, int KT, bool WIDE, bool CAP, bool SHAPED>
 static int launch_fa_form(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int n_work,
                      cudaStream_t s) {
   // the query tile, two key tiles, one or two value tiles, the probabilities, and room to align
@@ -453,19 +485,20 @@ static int launch_fa_form(const CUtensorMap& mq, const CUtensorMap& mk, const CU
   const size_t smem = panels * 128 * 128 + (2 + (KT == 64 ? 1 : 2)) * panels * KT * 128 + (size_t)(KT / 64) * 128 * 128 + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, KT, WIDE, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, KT, WIDE, CAP, SHAPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  attention_tcgen05_kernel<HD, KT, WIDE, CAP><<<n_work * p.n_heads, FA_THREADS, smem, s>>>(mq, mk, mv, p);
+  attention_tcgen05_kernel<HD, KT, WIDE, CAP, SHAPED><<<n_work * p.n_heads, FA_THREADS, smem, s>>>(mq, mk, mv, p);
   return launch_status();
 }
 
 template <int HD, int KT, bool WIDE>
 static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int n_work,
                      cudaStream_t s) {
-  if (p.cap_log2 > 0.0f) return launch_fa_form<HD, KT, WIDE, true>(mq, mk, mv, p, n_work, s);
-  return launch_fa_form<HD, KT, WIDE, false>(mq, mk, mv, p, n_work, s);
+  if (p.cap_log2 > 0.0f) return launch_fa_form<HD, KT, WIDE, true, false>(mq, mk, mv, p, n_work, s);
+  if (p.head_scale || p.bias_a) return launch_fa_form<HD, KT, WIDE, false, true>(mq, mk, mv, p, n_work, s);
+  return launch_fa_form<HD, KT, WIDE, false, false>(mq, mk, mv, p, n_work, s);
 }
 
 }  // namespace pkv
@@ -484,13 +517,18 @@ PKV_EXPORT int pkv_attention_tcgen05_rows() { return FA_BM; }
 
 // keep_first: with a window, keys below this position stay visible; softcap: scores are capped as
 // softcap * tanh(score * scale / softcap) (0: no cap).
-PKV_EXPORT int pkv_attention_prefill_tcgen05_sink(const void* qkv, int q_row_stride, int n_tokens, void* out,
-                                                  const void* k_pool, const void* v_pool, long long n_pages,
-                                                  const int32_t* block_table, int table_stride, const int32_t* seq_starts,
-                                                  const int32_t* first_pos, const int32_t* work_seq, const int32_t* work_q0,
-                                                  int n_work, int n_heads, int n_kv, int hd, int page_size, int window,
-                                                  int keep_first, float scale, float softcap, int* status, void* stream) {
+// head_scale, bias_a, bias_b: null, or float32 [n_heads] each (bias_a and bias_b together): the scaled score
+// is multiplied by head_scale[h] and loses bias_a[h] * ln(1 + bias_b[h] * distance); not together with a cap.
+PKV_EXPORT int pkv_attention_prefill_tcgen05_shaped(const void* qkv, int q_row_stride, int n_tokens, void* out,
+                                                    const void* k_pool, const void* v_pool, long long n_pages,
+                                                    const int32_t* block_table, int table_stride, const int32_t* seq_starts,
+                                                    const int32_t* first_pos, const int32_t* work_seq, const int32_t* work_q0,
+                                                    int n_work, int n_heads, int n_kv, int hd, int page_size, int window,
+                                                    int keep_first, float scale, float softcap, const float* head_scale,
+                                                    const float* bias_a, const float* bias_b, int* status, void* stream) {
   if (n_work <= 0) return 0;
+  if ((bias_a == nullptr) != (bias_b == nullptr)) return PKV_ERR_SIZE;
+  if (softcap > 0.0f && (head_scale || bias_a)) return PKV_ERR_LIMIT;
   if (!pkv_attention_tcgen05_supports(hd, page_size, q_row_stride)) return PKV_ERR_LIMIT;
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || window < 0 || keep_first < 0 || softcap < 0.0f || !(scale > 0.0f))
     return PKV_ERR_SIZE;
@@ -514,7 +552,7 @@ PKV_EXPORT int pkv_attention_prefill_tcgen05_sink(const void* qkv, int q_row_str
     if ((1 << i) == page_size) shift = i;
   FaParams p{(bf16*)out, block_table, table_stride, seq_starts, first_pos, work_seq, work_q0, n_heads, n_kv, page_size,
              shift, window, scale * 1.4426950408889634f, (int)pool_rows, keep_first, softcap * 1.4426950408889634f,
-             softcap > 0.0f ? 2.0f * scale / softcap * 1.4426950408889634f : 0.0f, status};
+             softcap > 0.0f ? 2.0f * scale / softcap * 1.4426950408889634f : 0.0f, head_scale, bias_a, bias_b, status};
   cudaStream_t s = (cudaStream_t)stream;
   // tiles of 64 keys (two blocks to an SM) wherever a page fits one
   if (page_size <= 64) {
@@ -525,6 +563,17 @@ PKV_EXPORT int pkv_attention_prefill_tcgen05_sink(const void* qkv, int q_row_str
   if (hd == 128 && wide) return launch_fa<128, 128, true>(map_q, map_k, map_v, p, n_work, s);
   if (hd == 128) return launch_fa<128, 128, false>(map_q, map_k, map_v, p, n_work, s);
   return launch_fa<64, 128, false>(map_q, map_k, map_v, p, n_work, s);
+}
+
+PKV_EXPORT int pkv_attention_prefill_tcgen05_sink(const void* qkv, int q_row_stride, int n_tokens, void* out,
+                                                  const void* k_pool, const void* v_pool, long long n_pages,
+                                                  const int32_t* block_table, int table_stride, const int32_t* seq_starts,
+                                                  const int32_t* first_pos, const int32_t* work_seq, const int32_t* work_q0,
+                                                  int n_work, int n_heads, int n_kv, int hd, int page_size, int window,
+                                                  int keep_first, float scale, float softcap, int* status, void* stream) {
+  return pkv_attention_prefill_tcgen05_shaped(qkv, q_row_stride, n_tokens, out, k_pool, v_pool, n_pages, block_table, table_stride,
+                                              seq_starts, first_pos, work_seq, work_q0, n_work, n_heads, n_kv, hd, page_size,
+                                              window, keep_first, scale, softcap, nullptr, nullptr, nullptr, status, stream);
 }
 
 PKV_EXPORT int pkv_attention_prefill_tcgen05(const void* qkv, int q_row_stride, int n_tokens, void* out,

@@ -356,22 +356,33 @@ def attention_prefill_tcgen05(qkv: torch.Tensor, out: torch.Tensor, k_pool: torc
                               block_table: torch.Tensor, seq_starts: torch.Tensor, first_pos: torch.Tensor,
                               work_seq: torch.Tensor, work_q0: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
                               page_size: int, window: int, scale: float, status: torch.Tensor, keep_first: int = 0,
-                              softcap: float = 0.0) -> None:
+                              softcap: float = 0.0, head_scale: torch.Tensor | None = None,
+                              distance_bias: tuple[torch.Tensor, torch.Tensor] | None = None) -> None:
     """Prefill attention on tcgen05 tensor cores with TMA page loads; writes the rows of its work
     items (blocks of 128 queries) into ``out``. With a window, keys below position ``keep_first``
-    stay visible; ``softcap`` ``c > 0`` caps the scores as ``c * tanh(score * scale / c)``."""
+    stay visible; ``softcap`` ``c > 0`` caps the scores as ``c * tanh(score * scale / c)``. Without a
+    cap, ``head_scale`` (float32 ``[n_heads]``) multiplies the scaled score of each head and
+    ``distance_bias`` ``(a, b)`` (float32 ``[n_heads]`` each) takes ``a_h * ln(1 + b_h * distance)`` off it."""
     for name, t in (("qkv", qkv), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
         _need(t, torch.bfloat16, name)
     for name, t in (("block_table", block_table), ("seq_starts", seq_starts), ("first_pos", first_pos),
                     ("work_seq", work_seq), ("work_q0", work_q0), ("status", status)):
         _need(t, torch.int32, name)
-    fn = _fn("attention_tcgen05", "pkv_attention_prefill_tcgen05_sink",
+    bias_a, bias_b = distance_bias if distance_bias is not None else (None, None)
+    for name, t in (("head_scale", head_scale), ("bias a", bias_a), ("bias b", bias_b)):
+        if t is not None:
+            _need(t, torch.float32, name)
+            if t.numel() != n_heads:
+                raise ValueError(f"{name} must have one entry per query head")
+    fn = _fn("attention_tcgen05", "pkv_attention_prefill_tcgen05_shaped",
              [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
-              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p])
+              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p,
+              c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(qkv), qkv.shape[1], qkv.shape[0], _ptr(out), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0],
               _ptr(block_table), block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq),
               _ptr(work_q0), work_seq.numel(), n_heads, n_kv, head_dim, page_size, int(window), int(keep_first),
-              float(scale), float(softcap), _ptr(status), _stream()), "attention_prefill_tcgen05")
+              float(scale), float(softcap), _ptr(head_scale), _ptr(bias_a), _ptr(bias_b), _ptr(status), _stream()),
+           "attention_prefill_tcgen05")
 
 
 _DECODE_TMA_BLOCKS: dict[tuple[int, bool], int] = {}

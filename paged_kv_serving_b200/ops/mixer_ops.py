@@ -540,14 +540,15 @@ def attention_sink_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
                        seq_starts: torch.Tensor, first_pos: torch.Tensor, work_seq: torch.Tensor, work_q0: torch.Tensor,
                        n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int, window: int, keep_first: int, scale: float,
                        softcap: float, status: torch.Tensor, num_splits: int = 1, head_scale: torch.Tensor | None = None,
-                       distance_bias: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
+                       distance_bias: tuple[torch.Tensor, torch.Tensor] | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """``attention_sink`` on the tensor cores (``mma.sync``, bfloat16 operands, float32 scores and
     accumulators) for head sizes that are multiples of 16. The rows of an (entry, key/value head)
     are (token, head in group) pairs, ``row = token * (H / G) + head in group``; the work list is in
     blocks of ``attention_sink_mma_rows()`` rows (``work_q0``: the block's first row) and must
     cover every token of the step when ``num_splits`` > 1: every block's key range is then
     cut into that many shares (at most 8) that run side by side and are merged by a second
-    kernel (for steps of few rows over long contexts)."""
+    kernel (for steps of few rows over long contexts). With ``out`` the rows of the work list are
+    written there (another kernel may serve the step's other rows) instead of into a new tensor."""
     _need(q, torch.bfloat16, "q"); _need(k_pool, torch.bfloat16, "k_pool"); _need(v_pool, torch.bfloat16, "v_pool")
     for name, t in (("block_table", block_table), ("seq_starts", seq_starts), ("first_pos", first_pos),
                     ("work_seq", work_seq), ("work_q0", work_q0)):
@@ -555,7 +556,12 @@ def attention_sink_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
     tokens = q.shape[0]
     if q.shape[1] < n_heads * dim:
         raise ValueError("q is narrower than its heads")
-    out = _empty((tokens, n_heads * vdim), q.dtype, q.device)
+    if out is None:
+        out = _empty((tokens, n_heads * vdim), q.dtype, q.device)
+    else:
+        _need(out, torch.bfloat16, "out")
+        if tuple(out.shape) != (tokens, n_heads * vdim):
+            raise ValueError("out must have a row per token and the width of the heads' values")
     num_pages = k_pool.numel() // (n_kv * page_size * dim)
     part_o = part_ml = None
     if num_splits > 1:

@@ -51,12 +51,17 @@ class SinkWindowAttention(Part):
     tokens as further tiles in front of the window's and cap the scores in their softmax; in
     bfloat16 with other head sizes that are multiples of 16 (keys and values may differ) the
     ``mma.sync`` kernel ``ops.mixer_ops.attention_sink_mma``; for every other size and for float32
-    the general kernel ``ops.mixer_ops.attention_sink``.
+    the general kernel ``ops.mixer_ops.attention_sink``. With a temperature or a distance bias (and
+    no cap) and heads of 64 or 128, a step that holds a long entry gives its long entries to the tcgen05
+    kernel, which applies both in its softmax, and the short ones to the ``mma.sync`` kernel.
     """
 
     graph_safe = True
     #: Set to False to keep every step on the general kernel (tests compare the two).
     USE_TENSOR_CORES = True
+    #: With a temperature or a distance bias: entries of at least this many tokens go to the tcgen05 kernel
+    #: (blocks of 128 queries of one head), shorter ones to the ``mma.sync`` kernel (64 rows of a head group).
+    SHAPED_TCGEN05_MIN_TOKENS = 64
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
                  rotary: ScaledRotaryFrequencies | None = None, unit_norm: bool = True, eps: float = 1e-6,
@@ -136,6 +141,9 @@ class SinkWindowAttention(Part):
         if self._fast(ctx, ctx.groups[binding.group].page_size):
             self._plan_fast(ctx, ctx.groups[binding.group].page_size)
             return
+        if self._shaped_split(ctx, ctx.groups[binding.group].page_size):
+            self._plan_shaped(ctx, ctx.groups[binding.group].page_size)
+            return
         if self._mma(ctx):
             self._plan_mma(ctx)
             return
@@ -162,6 +170,70 @@ class SinkWindowAttention(Part):
             self._fast_ok[key] = (ops.attention_tcgen05_supports(self.dim, page_size, self.fused_rows)
                                   and ops.attention_decode_tma_supports(self.dim, page_size, self.fused_rows))
         return self._fast_ok[key]
+
+    def _shaped_split(self, ctx: StepContext, page_size: int) -> bool:
+        """Whether this step goes to two kernels: the tcgen05 kernel (which knows the head temperature and
+        the distance bias, not the cap) for entries of at least ``SHAPED_TCGEN05_MIN_TOKENS`` tokens and the
+        ``mma.sync`` kernel for the others. Only for mixers with a temperature or a bias, and only in steps
+        that hold such an entry; decode steps stay with the ``mma.sync`` kernel and its shares."""
+        if not (self.head_temperature or self.distance_bias) or self.softcap or self.dim != self.vdim or not self._mma(ctx):
+            return False
+        if max(ctx.seq_lens) < self.SHAPED_TCGEN05_MIN_TOKENS:
+            return False
+        key = ("shaped", page_size)
+        if key not in self._fast_ok:
+            self._fast_ok[key] = ops.attention_tcgen05_supports(self.dim, page_size, self.fused_rows)
+        return self._fast_ok[key]
+
+    def _shaped_key(self, page_size: int) -> str:
+        return (f"sink_attention/shaped/h{self.n_heads}k{self.n_kv_heads}d{self.dim}w{self.window or 0}s{self.keep_first}"
+                f"p{page_size}")
+
+    def _plan_shaped(self, ctx: StepContext, page_size: int) -> None:
+        """Work lists of a step that two kernels share: blocks of 128 queries of the long entries, heaviest
+        first, and blocks of (token, head in group) rows of the short ones."""
+        key = self._shaped_key(page_size)
+        if key in ctx.scratch:
+            return
+        lens = np.asarray(ctx.seq_lens, dtype=np.int64)
+        first = np.asarray(ctx.first_positions, dtype=np.int64)
+        long_entries = np.nonzero(lens >= self.SHAPED_TCGEN05_MIN_TOKENS)[0]
+        short_entries = np.nonzero(lens < self.SHAPED_TCGEN05_MIN_TOKENS)[0]
+
+        def blocks_of(entries, rows_of_entry, block_rows):
+            blocks = (rows_of_entry + block_rows - 1) // block_rows
+            seq = np.repeat(entries, blocks)
+            starts = np.cumsum(blocks) - blocks
+            return seq, (np.arange(int(blocks.sum()), dtype=np.int64) - np.repeat(starts, blocks)) * block_rows
+
+        long_seq, long_q0 = blocks_of(long_entries, lens[long_entries], ops.attention_tcgen05_rows())
+        cost = first[long_seq] + long_q0
+        if self.window:
+            cost = np.minimum(cost, self.window + self.keep_first)
+        order = np.argsort(-cost, kind="stable")
+        short_seq, short_q0 = blocks_of(short_entries, lens[short_entries] * self.group_size, mixer_ops.attention_sink_mma_rows())
+        names = {k: f"{key}/{k}" for k in ("long_seq", "long_q0", "short_seq", "short_q0")}
+        ctx.arena.add(names["long_seq"], long_seq[order])
+        ctx.arena.add(names["long_q0"], long_q0[order])
+        ctx.arena.add(names["short_seq"], short_seq if len(short_seq) else [0])
+        ctx.arena.add(names["short_q0"], short_q0 if len(short_q0) else [0])
+        ctx.scratch[key] = {"names": names, "n_short": int(len(short_seq))}
+
+    def _attend_shaped(self, qkv: torch.Tensor, ctx: StepContext, group, k_pool, v_pool, bias) -> torch.Tensor:
+        plan = ctx.scratch[self._shaped_key(group.page_size)]
+        names = plan["names"]
+        out = arena.empty((qkv.shape[0], self.n_heads * self.vdim), qkv.dtype, qkv.device)
+        table, starts, first = ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS)
+        ops.attention_prefill_tcgen05(qkv, out, k_pool, v_pool, table, starts, first, ctx.ints(names["long_seq"]),
+                                      ctx.ints(names["long_q0"]), self.n_heads, self.n_kv_heads, self.dim, group.page_size,
+                                      self.window or 0, self.scale, ctx.status, keep_first=self.keep_first,
+                                      head_scale=self.temp, distance_bias=bias)
+        if plan["n_short"]:
+            mixer_ops.attention_sink_mma(
+                qkv, k_pool, v_pool, table, starts, first, ctx.ints(names["short_seq"]), ctx.ints(names["short_q0"]),
+                self.n_heads, self.n_kv_heads, self.dim, self.vdim, group.page_size, self.window or 0, self.keep_first,
+                self.scale, self.softcap, ctx.status, head_scale=self.temp, distance_bias=bias, out=out)
+        return out
 
     def _mma(self, ctx: StepContext) -> bool:
         """Whether the ``mma.sync`` kernel serves this mixer in this step (when ``_fast`` does not)."""
@@ -301,6 +373,9 @@ class SinkWindowAttention(Part):
         bias = (self.r1, self.r2) if self.distance_bias else None
         if self._fast(ctx, group.page_size):
             return gemm.linear(self._attend_fast(qkv, ctx, group, k_pool, v_pool), self.o, out_dtype=torch.float32, few_rows_f32=True)
+        if self._shaped_split(ctx, group.page_size):
+            return gemm.linear(self._attend_shaped(qkv, ctx, group, k_pool, v_pool, bias), self.o, out_dtype=torch.float32,
+                               few_rows_f32=True)
         if self._mma(ctx):
             attended = mixer_ops.attention_sink_mma(
                 qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),

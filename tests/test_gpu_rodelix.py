@@ -645,6 +645,53 @@ def test_tensor_core_attention_kernels_serve_sizes_in_steps_of_16_and_agree_with
     close(results[False], want, "bfloat16", "general kernels")
 
 
+@pytest.mark.parametrize("size,page,dim,heads,kv_heads", [(70, 16, 64, 4, 2), (33, 64, 128, 2, 1), (129, 8, 64, 3, 3), (None, 16, 64, 2, 1)])
+def test_long_entries_on_tcgen05_beside_short_ones_with_temperature_and_distance_bias(size, page, dim, heads, kv_heads, monkeypatch):
+    """Heads of 64 and 128 in bfloat16: a step that holds a long entry gives it to the tcgen05 kernel and its
+    short entries to the ``mma.sync`` kernel. Scores are peaked so that a window off by one, a bias or a
+    temperature left out (one head's is negative) would change whole rows; two requests run side by side."""
+    from paged_kv_serving_b200 import ops
+
+    config = _model([_layer(_window(heads, kv_heads, dim, dim, size=size, scale=0.6), None)], vocab=90, width=48, mult=1.0)
+    tensors = random_tensors(config, seed=71, scale=2.0)
+    for name in tensors:
+        if name.endswith(("r1", "r2")):
+            tensors[name] = tensors[name] * 0.3
+        if name.endswith("temp"):
+            tensors[name] = tensors[name].clone()
+            tensors[name][0] = -tensors[name][0].abs()
+    first, second = tokens_for(config, 330, seed=72), tokens_for(config, 200, seed=73)
+    want = {"a": plain_logits(config, tensors, first), "b": plain_logits(config, tensors, second)}
+    if size is not None:
+        shifted = plain_logits(_model([_layer(_window(heads, kv_heads, dim, dim, size=size + 1, scale=0.6), None)], vocab=90, width=48,
+                                      mult=1.0), tensors, first)
+        assert np.abs(shifted - want["a"]).max() > 0.05 * want["a"].std(), "the test cannot tell a window one longer apart"
+    calls = {"tcgen05": 0}
+    real = ops.attention_prefill_tcgen05
+
+    def counted(*args, **kwargs):
+        calls["tcgen05"] += 1
+        return real(*args, **kwargs)
+
+    monkeypatch.setattr(ops, "attention_prefill_tcgen05", counted)
+    session = session_for(config, tensors, "bfloat16", max_tokens=640, page=page)
+    got = {"a": [], "b": []}
+    # a: 200 tokens | 3 | 64 | 1 ... ; b: 5 | 130 | 2 | 63 (below the border: the other kernel alone)
+    steps = [[("a", 0, 200), ("b", 0, 5)], [("a", 200, 203), ("b", 5, 135)], [("a", 203, 267), ("b", 135, 137)],
+             [("a", 267, 268), ("b", 137, 200)], [("a", 268, 330)]]
+    for step in steps:
+        entries = [{"id": r, "tokens": (first if r == "a" else second)[lo:hi], "want": list(range(hi - lo))} for r, lo, hi in step]
+        rows = session.step(entries)
+        at = 0
+        for r, lo, hi in step:
+            got[r].append(rows[at:at + hi - lo])
+            at += hi - lo
+    assert calls["tcgen05"] == 3, "steps with an entry of 64 tokens or more did not reach the tcgen05 kernel"
+    for r in ("a", "b"):
+        error = row_errors(np.concatenate(got[r]), want[r])
+        assert float(np.median(error)) <= 0.05 and float(error.max()) <= 0.5, f"request {r}: rows off by up to {error.max():.3e}"
+
+
 # --- seeded random configurations -----------------------------------------------------------------------
 
 
