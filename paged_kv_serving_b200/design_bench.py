@@ -91,7 +91,7 @@ def rodelix_config(size: str) -> dict:
     linear = {"type": "lightning", "mixer": {"heads": z["l_heads"], "dim": z["l_dim"], "vdim": z["l_vdim"], "decay": decays}}
     dense = {"kind": "dense", "ff": z["ff"]}
     layers = [{**latent, "mlp": dense}, {**linear, "mlp": dense}, {**window, "mlp": dense}, {**linear, "mlp": dense}]
-    return {"architecture": "Rodelix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.7,
+    return {"architecture": "Rodelix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.5,
             "logit_softcap": 30.0, "layers": layers}
 
 
