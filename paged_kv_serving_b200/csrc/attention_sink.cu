@@ -8,6 +8,9 @@
 //                   square, writes queries back in place and keys into the key pool; blends a
 //                   value head with the same token's value of another layer,
 //                   v <- (1 - lambda) v + lambda v_other, and writes it into the value pool.
+//                   A bias per column may be added to the projections first, and the norm may
+//                   instead be one over all of a token's query columns (and one over all its key
+//                   columns) with a weight per column, applied before the rotation.
 //   attention_sink  float32-arithmetic attention for any sizes, float32 or bfloat16 storage:
 //                   score = q.k * scale, then cap * tanh(score / cap); query position i sees key
 //                   j when j <= i and (i - j < window or j < keep_first); softmax; weighted sum
@@ -35,7 +38,9 @@ struct PrepareParams {
   int rot_dims;           // 0: no rotation
   float rot_factor;
   float eps;
-  int unit_norm;          // divide query and key heads by their root mean square
+  int unit_norm;          // 1: divide query and key heads by their root mean square, after the rotation;
+                          // 2: divide all query columns of a token by their joint root mean square (the key
+                          //    columns by theirs) and multiply by a weight per column, before the rotation
   int page_size;
   long long pool_slots;   // pages * page_size
   int ld_other;           // row stride of the other layer's values
@@ -44,7 +49,7 @@ struct PrepareParams {
 template <typename A, typename C>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 qkv_prepare_kernel(A* __restrict__ qkv, const int32_t* __restrict__ positions, const float* __restrict__ freq,
-                   const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                   const float* __restrict__ q_weight, const float* __restrict__ k_weight, const float* __restrict__ bias,
                    const A* __restrict__ v_other, const float* __restrict__ lambda, A* __restrict__ v_keep,
                    C* __restrict__ k_pool, C* __restrict__ v_pool, const int32_t* __restrict__ slots, PrepareParams p,
                    int* __restrict__ status) {
@@ -65,12 +70,43 @@ qkv_prepare_kernel(A* __restrict__ qkv, const int32_t* __restrict__ positions, c
   const int offset = slot >= 0 ? (int)(slot % p.page_size) : 0;
   const int half = p.rot_dims >> 1;
   const int qk_heads = p.n_heads + p.n_kv;
+  const bool joint = p.unit_norm == 2;
+  float inv_q = 1.0f, inv_k = 1.0f;
+  if (joint) {
+    float* scratch = prep_smem + SK_WARPS * p.dim;      // [32]
+    const int q_cols = p.n_heads * p.dim, k_cols = p.n_kv * p.dim;
+    float sq = 0.0f;
+    for (int c = threadIdx.x; c < q_cols; c += blockDim.x) {
+      const float v = to_float(row[c]) + (bias ? bias[c] : 0.0f);
+      sq = fmaf(v, v, sq);
+    }
+    inv_q = 1.0f / sqrtf(block_sum(sq, scratch) / (float)q_cols + p.eps);
+    sq = 0.0f;
+    for (int c = threadIdx.x; c < k_cols; c += blockDim.x) {
+      const float v = to_float(row[q_cols + c]) + (bias ? bias[q_cols + c] : 0.0f);
+      sq = fmaf(v, v, sq);
+    }
+    inv_k = 1.0f / sqrtf(block_sum(sq, scratch) / (float)k_cols + p.eps);
+    __syncthreads();
+  }
   for (int unit = warp; unit < qk_heads + p.n_kv; unit += SK_WARPS) {
     if (unit < qk_heads) {
       // a query head (written back in place) or a key head (written to the pool)
       A* x = row + (size_t)unit * p.dim;
+      const float* b = bias ? bias + (size_t)unit * p.dim : nullptr;
+      // with the joint norm: the factor of this head's columns before the rotation
+      const float pre = joint ? (unit < p.n_heads ? inv_q : inv_k) : 1.0f;
+      const float* pre_w = !joint ? nullptr
+                                  : (unit < p.n_heads ? (q_weight ? q_weight + (size_t)unit * p.dim : nullptr)
+                                                      : (k_weight ? k_weight + (size_t)(unit - p.n_heads) * p.dim : nullptr));
+      for (int d = lane; d < p.dim; d += 32) {
+        float v = to_float(x[d]) + (b ? b[d] : 0.0f);
+        if (joint) v = v * pre * (pre_w ? pre_w[d] : 1.0f);
+        buf[d] = v;
+      }
+      __syncwarp();
       for (int i = lane; i < half; i += 32) {
-        const float u = to_float(x[i]), v = to_float(x[i + half]);
+        const float u = buf[i], v = buf[i + half];
         float sn, cs;
         sincosf(pos * freq[i], &sn, &cs);
         sn *= p.rot_factor;
@@ -78,22 +114,23 @@ qkv_prepare_kernel(A* __restrict__ qkv, const int32_t* __restrict__ positions, c
         buf[i] = u * cs - v * sn;
         buf[i + half] = v * cs + u * sn;
       }
-      for (int d = p.rot_dims + lane; d < p.dim; d += 32) buf[d] = to_float(x[d]);
       __syncwarp();
       float inv = 1.0f;
-      if (p.unit_norm) {
+      if (p.unit_norm == 1) {
         float sq = 0.0f;
         for (int d = lane; d < p.dim; d += 32) sq = fmaf(buf[d], buf[d], sq);
         sq = warp_sum(sq);
         inv = 1.0f / sqrtf(sq / (float)p.dim + p.eps);
       }
+      const float* q_w = joint ? nullptr : q_weight;
+      const float* k_w = joint ? nullptr : k_weight;
       // (the norm's weight, one per coordinate and the same for every head, where the mixer has one)
       if (unit < p.n_heads) {
-        for (int d = lane; d < p.dim; d += 32) x[d] = from_float<A>(buf[d] * inv * (q_weight ? q_weight[d] : 1.0f));
+        for (int d = lane; d < p.dim; d += 32) x[d] = from_float<A>(buf[d] * inv * (q_w ? q_w[d] : 1.0f));
       } else if (slot >= 0) {
         const int kvh = unit - p.n_heads;
         C* dst = k_pool + (((size_t)page * p.n_kv + kvh) * p.page_size + offset) * p.dim;
-        for (int d = lane; d < p.dim; d += 32) dst[d] = from_float<C>(buf[d] * inv * (k_weight ? k_weight[d] : 1.0f));
+        for (int d = lane; d < p.dim; d += 32) dst[d] = from_float<C>(buf[d] * inv * (k_w ? k_w[d] : 1.0f));
       }
       __syncwarp();
     } else {
@@ -103,8 +140,9 @@ qkv_prepare_kernel(A* __restrict__ qkv, const int32_t* __restrict__ positions, c
       A* keep = v_keep ? v_keep + ((size_t)t * p.n_kv + kvh) * p.vdim : nullptr;
       C* dst = slot >= 0 ? v_pool + (((size_t)page * p.n_kv + kvh) * p.page_size + offset) * p.vdim : nullptr;
       const float lam = other ? lambda[0] : 0.0f;
+      const float* b = bias ? bias + (size_t)qk_heads * p.dim + (size_t)kvh * p.vdim : nullptr;
       for (int d = lane; d < p.vdim; d += 32) {
-        float val = to_float(v[d]);
+        float val = to_float(v[d]) + (b ? b[d] : 0.0f);
         if (other) val = (1.0f - lam) * val + lam * to_float(other[d]);
         if (keep) keep[d] = from_float<A>(val);
         if (dst) dst[d] = from_float<C>(val);
@@ -566,24 +604,26 @@ using namespace pkv;
 
 template <typename A, typename C>
 static int launch_prepare(void* qkv, const int32_t* positions, const float* freq, const float* q_weight, const float* k_weight,
-                          const void* v_other, const float* lambda,
+                          const float* bias, const void* v_other, const float* lambda,
                           void* v_keep, void* k_pool, void* v_pool, const int32_t* slots, const PrepareParams& p, int tokens,
                           int* status, cudaStream_t s) {
-  const size_t smem = (size_t)SK_WARPS * p.dim * sizeof(float);
+  const size_t smem = ((size_t)SK_WARPS * p.dim + 32) * sizeof(float);
   return launch_kernel(qkv_prepare_kernel<A, C>, dim3(tokens), dim3(SK_WARPS * 32), smem, s, true, 0, (A*)qkv, positions, freq,
-                       q_weight, k_weight, (const A*)v_other, lambda, (A*)v_keep, (C*)k_pool, (C*)v_pool, slots, p, status);
+                       q_weight, k_weight, bias, (const A*)v_other, lambda, (A*)v_keep, (C*)k_pool, (C*)v_pool, slots, p, status);
 }
 
 // qkv [tokens, ld]: H query heads of `dim`, G key heads of `dim`, G value heads of `vdim`.
 // freq [rot_dims / 2] float32 (null with rot_dims 0). q_weight, k_weight: float32 [dim] factors on
-// the unit-norm query and key heads, or null. v_other: the values [tokens, ld_other] of
+// the unit-norm query and key heads, or null; with unit_norm 2 (one norm over all query columns, one
+// over all key columns, before the rotation) float32 [H * dim] and [G * dim]. bias: float32 [H dim + G
+// dim + G vdim] added to the columns first, or null. v_other: the values [tokens, ld_other] of
 // another layer to blend with, weight lambda[0] (a float on the device), or null. v_keep: where
 // to leave this layer's values [tokens, G * vdim] as they are cached, or null.
 // k_pool [pages][G][page_size][dim], v_pool [pages][G][page_size][vdim]; slots: int32 per token,
 // negative (or null): nothing is cached for it.
 PKV_EXPORT int pkv_qkv_prepare(void* qkv, int act_dtype, int ld, const int32_t* positions, const float* freq, int rot_dims,
                                float rot_factor, float eps, int unit_norm, const float* q_weight, const float* k_weight,
-                               const void* v_other, int ld_other,
+                               const float* bias, const void* v_other, int ld_other,
                                const float* lambda, void* v_keep, void* k_pool, void* v_pool, int cache_dtype,
                                const int32_t* slots, long long pool_slots, int tokens, int n_heads, int n_kv, int dim, int vdim,
                                int page_size, int* status, void* stream) {
@@ -595,7 +635,7 @@ PKV_EXPORT int pkv_qkv_prepare(void* qkv, int act_dtype, int ld, const int32_t* 
   PrepareParams p{ld, n_heads, n_kv, dim, vdim, rot_dims, rot_factor, eps, unit_norm, page_size, pool_slots, ld_other};
   cudaStream_t s = (cudaStream_t)stream;
 #define PKV_PREP(A, C) \
-  return launch_prepare<A, C>(qkv, positions, freq, q_weight, k_weight, v_other, lambda, v_keep, k_pool, v_pool, slots, p, tokens, status, s)
+  return launch_prepare<A, C>(qkv, positions, freq, q_weight, k_weight, bias, v_other, lambda, v_keep, k_pool, v_pool, slots, p, tokens, status, s)
   if (act_dtype == PKV_F32 && cache_dtype == PKV_F32) PKV_PREP(float, float);
   if (act_dtype == PKV_BF16 && cache_dtype == PKV_BF16) PKV_PREP(bf16, bf16);
   if (act_dtype == PKV_F32 && cache_dtype == PKV_BF16) PKV_PREP(float, bf16);

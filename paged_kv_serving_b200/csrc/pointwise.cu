@@ -341,6 +341,156 @@ __global__ void softcap_kernel(float* __restrict__ x, long long total, float cap
   if (i < total) x[i] = cap * tanhf(x[i] / cap);
 }
 
+// Router with sigmoid scores and groups of experts. score_e = sigmoid(logit_e); an expert is chosen
+// by score_e + correction_e (the choice score), its weight comes from score_e alone. The experts
+// form `groups` equal groups of neighbours; a group's score is the sum of its two largest choice
+// scores (of its one, in groups of one), and only experts of the `keep` best groups can be chosen.
+// The `top` allowed experts with the largest choice scores are chosen (the lower index wins a tie);
+// their weights are score / (sum of the chosen scores + 1e-20) * scale, every other weight is zero.
+// A thread a token; up to 64 groups.
+__global__ void route_scored_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ correction,
+                                    float* __restrict__ weights, int tokens, int experts, int top, int groups, int keep,
+                                    float scale) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= tokens) return;
+  const float* z = logits + (size_t)t * ld;
+  float* w = weights + (size_t)t * experts;
+  const int per_group = experts / groups;
+  unsigned long long allowed = ~0ull;
+  if (keep < groups) {
+    allowed = 0ull;
+    for (int k = 0; k < keep; ++k) {
+      float best = -INFINITY;
+      int best_g = -1;
+      for (int g = 0; g < groups; ++g) {
+        if ((allowed >> g) & 1ull) continue;
+        float first = -INFINITY, second = -INFINITY;
+        for (int e = g * per_group; e < (g + 1) * per_group; ++e) {
+          const float c = 1.0f / (1.0f + expf(-z[e])) + (correction ? correction[e] : 0.0f);
+          if (c > first) { second = first; first = c; }
+          else if (c > second) second = c;
+        }
+        const float score = per_group > 1 ? first + second : first;
+        if (best_g < 0 || score > best) { best = score; best_g = g; }
+      }
+      if (best_g < 0) break;
+      allowed |= 1ull << best_g;
+    }
+  }
+  for (int e = 0; e < experts; ++e) w[e] = 0.0f;
+  float last = INFINITY;
+  int last_e = -1;
+  float chosen_sum = 0.0f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY, best_s = 0.0f;
+    int best_e = -1;
+    for (int e = 0; e < experts; ++e) {
+      if (!((allowed >> (e / per_group)) & 1ull)) continue;
+      const float s = 1.0f / (1.0f + expf(-z[e]));
+      const float c = s + (correction ? correction[e] : 0.0f);
+      const bool after_last = c < last || (c == last && e > last_e);   // order: choice score down, index up
+      if (after_last && (best_e < 0 || c > best)) { best = c; best_e = e; best_s = s; }
+    }
+    if (best_e < 0) break;
+    w[best_e] = -1.0f - best_s;              // marked as chosen (a score may be 0): -1 - score
+    chosen_sum += best_s;
+    last = best;
+    last_e = best_e;
+  }
+  const float denom = chosen_sum + 1e-20f;
+  for (int e = 0; e < experts; ++e)
+    if (w[e] < 0.0f) w[e] = (-1.0f - w[e]) / denom * scale;
+}
+
+// A gated feed-forward's middle step with biases: gu[t, :] holds the gate columns [n] and, `up_at`
+// columns further on, the up columns; out[t, c] = act(gate + gate_bias[c]) * (up + up_bias[c]).
+template <typename X>
+__global__ void gated_bias_act_kernel(const X* __restrict__ gu, int ld, int up_at, const float* __restrict__ gate_bias,
+                                      const float* __restrict__ up_bias, X* __restrict__ out, int tokens, int n, int act) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)tokens * n) return;
+  const int t = (int)(i / n), c = (int)(i - (long long)t * n);
+  const X* row = gu + (size_t)t * ld;
+  const float g = to_float(row[c]) + (gate_bias ? gate_bias[c] : 0.0f);
+  const float u = to_float(row[up_at + c]) + (up_bias ? up_bias[c] : 0.0f);
+  out[(size_t)t * n + c] = from_float<X>(activate(g, act) * u);
+}
+
+// hidden[t] += delta[t] (when given); out[t] = [hidden[t] | other[t]] in the type of out: the
+// stream beside a second float32 matrix of the same shape, as the operand of one product.
+template <typename D, typename O>
+__global__ void pair_rows_kernel(float* __restrict__ hidden, const D* __restrict__ delta, const float* __restrict__ other,
+                                 O* __restrict__ out, long long total, int cols) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / cols;
+  const int c = (int)(i - t * cols);
+  float v = hidden[i];
+  if (delta) { v += to_float(delta[i]); hidden[i] = v; }
+  out[t * 2 * cols + c] = from_float<O>(v);
+  out[t * 2 * cols + cols + c] = from_float<O>(other[i]);
+}
+
+// hidden[t, c] = value[t, c] + bias[c]
+__global__ void assign_bias_kernel(float* __restrict__ hidden, const float* __restrict__ value, const float* __restrict__ bias,
+                                   long long total, int cols) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  hidden[i] = value[i] + (bias ? bias[i % cols] : 0.0f);
+}
+
+// Two float32 updates of the same shape become one. With weights: out = fa * a / rms(a) * wa + fb * b /
+// rms(b) * wb (each divided by its own root mean square over the row); without: out = fa * a + fb * b.
+// One block a row.
+__global__ void combine_pair_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ wa,
+                                    const float* __restrict__ wb, float fa, float fb, float eps, float* __restrict__ out, int d) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
+  __shared__ float scratch[32];
+  const size_t at = (size_t)blockIdx.x * d;
+  float inv_a = 1.0f, inv_b = 1.0f;
+  if (wa) {
+    float sa = 0.0f, sb = 0.0f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+      sa = fmaf(a[at + c], a[at + c], sa);
+      sb = fmaf(b[at + c], b[at + c], sb);
+    }
+    sa = block_sum(sa, scratch);
+    sb = block_sum(sb, scratch);
+    inv_a = 1.0f / sqrtf(sa / (float)d + eps);
+    inv_b = 1.0f / sqrtf(sb / (float)d + eps);
+  }
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float x = wa ? a[at + c] * inv_a * wa[c] : a[at + c];
+    const float y = wb ? b[at + c] * inv_b * wb[c] : b[at + c];
+    out[at + c] = fa * x + fb * y;
+  }
+}
+
+// out[t, h * vdim + j] = x[t, h * vdim + j] * sigmoid(gate[t * gate_ld + h]) * factor: one gate per token and
+// head (or none: the factor alone). `out` may be `x` itself, or rows with a stride of their own.
+template <typename X>
+__global__ void head_gate_kernel(const X* __restrict__ x, const X* __restrict__ gate, int gate_ld, X* __restrict__ out,
+                                 int out_ld, long long total, int heads, int vdim, float factor) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / ((long long)heads * vdim);
+  const int c = (int)(i - t * heads * vdim);
+  float f = factor;
+  if (gate) f = factor / (1.0f + expf(-to_float(gate[t * gate_ld + c / vdim])));
+  out[t * out_ld + c] = from_float<X>(to_float(x[i]) * f);
+}
+
 }  // namespace pkv
 
 using namespace pkv;
@@ -513,4 +663,75 @@ PKV_EXPORT int pkv_softcap(float* x, long long total, float cap, void* stream) {
   if (total <= 0) return 0;
   if (!(cap > 0.0f)) return PKV_ERR_SIZE;
   return launch_kernel(softcap_kernel, dim3(blocks_for(total, 256)), dim3(256), 0, (cudaStream_t)stream, true, 0, x, total, cap);
+}
+
+PKV_EXPORT int pkv_route_scored(const float* logits, int ld, const float* correction, float* weights, int tokens, int experts,
+                                int top, int groups, int keep, float scale, void* stream) {
+  if (tokens <= 0) return 0;
+  if (experts < 1 || top < 1 || top > experts || ld < experts || groups < 1 || groups > 64 || experts % groups || keep < 1 ||
+      keep > groups || top > experts / groups * keep)
+    return PKV_ERR_SIZE;
+  return launch_kernel(route_scored_kernel, dim3(blocks_for(tokens, 32)), dim3(32), 0, (cudaStream_t)stream, true, 0, logits, ld,
+                       correction, weights, tokens, experts, top, groups, keep, scale);
+}
+
+PKV_EXPORT int pkv_gated_bias_act(const void* gu, int dtype, int ld, int up_at, const float* gate_bias, const float* up_bias,
+                                  void* out, int tokens, int n, int act, void* stream) {
+  const long long total = (long long)tokens * n;
+  if (total <= 0) return 0;
+  if (act < 0 || act > ACT_LAST || up_at < n || ld < up_at + n) return PKV_ERR_SIZE;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == PKV_F32)
+    return launch_kernel(gated_bias_act_kernel<float>, dim3(blocks_for(total, 256)), dim3(256), 0, s, true, 0, (const float*)gu, ld,
+                         up_at, gate_bias, up_bias, (float*)out, tokens, n, act);
+  if (dtype == PKV_BF16)
+    return launch_kernel(gated_bias_act_kernel<bf16>, dim3(blocks_for(total, 256)), dim3(256), 0, s, true, 0, (const bf16*)gu, ld,
+                         up_at, gate_bias, up_bias, (bf16*)out, tokens, n, act);
+  return PKV_ERR_DTYPE;
+}
+
+PKV_EXPORT int pkv_pair_rows(float* hidden, const void* delta, int delta_dtype, const float* other, void* out, int out_dtype,
+                             long long rows, int cols, void* stream) {
+  const long long total = rows * cols;
+  if (total <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+#define PKV_PR(D, O) return launch_kernel(pair_rows_kernel<D, O>, dim3(blocks_for(total, 256)), dim3(256), 0, s, true, 0, hidden, (const D*)delta, other, (O*)out, total, cols)
+  if (!delta) delta_dtype = PKV_F32;
+  if (delta_dtype == PKV_F32 && out_dtype == PKV_F32) { PKV_PR(float, float); }
+  if (delta_dtype == PKV_F32 && out_dtype == PKV_BF16) { PKV_PR(float, bf16); }
+  if (delta_dtype == PKV_BF16 && out_dtype == PKV_BF16) { PKV_PR(bf16, bf16); }
+  if (delta_dtype == PKV_BF16 && out_dtype == PKV_F32) { PKV_PR(bf16, float); }
+#undef PKV_PR
+  return PKV_ERR_DTYPE;
+}
+
+PKV_EXPORT int pkv_assign_bias(float* hidden, const float* value, const float* bias, long long rows, int cols, void* stream) {
+  const long long total = rows * cols;
+  if (total <= 0) return 0;
+  return launch_kernel(assign_bias_kernel, dim3(blocks_for(total, 256)), dim3(256), 0, (cudaStream_t)stream, true, 0, hidden, value,
+                       bias, total, cols);
+}
+
+PKV_EXPORT int pkv_combine_pair(const float* a, const float* b, const float* wa, const float* wb, float fa, float fb, float eps,
+                                float* out, int rows, int d, void* stream) {
+  if (rows <= 0) return 0;
+  if (d <= 0 || ((wa == nullptr) != (wb == nullptr))) return PKV_ERR_SIZE;
+  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+  return launch_kernel(combine_pair_kernel, dim3(rows), dim3(threads), 0, (cudaStream_t)stream, true, 0, a, b, wa, wb, fa, fb, eps,
+                       out, d);
+}
+
+PKV_EXPORT int pkv_head_gate(const void* x, const void* gate, int dtype, int gate_ld, void* out, int out_ld, int tokens, int heads,
+                             int vdim, float factor, void* stream) {
+  const long long total = (long long)tokens * heads * vdim;
+  if (total <= 0) return 0;
+  if ((gate && gate_ld < heads) || out_ld < heads * vdim) return PKV_ERR_SIZE;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == PKV_F32)
+    return launch_kernel(head_gate_kernel<float>, dim3(blocks_for(total, 256)), dim3(256), 0, s, true, 0, (const float*)x,
+                         (const float*)gate, gate_ld, (float*)out, out_ld, total, heads, vdim, factor);
+  if (dtype == PKV_BF16)
+    return launch_kernel(head_gate_kernel<bf16>, dim3(blocks_for(total, 256)), dim3(256), 0, s, true, 0, (const bf16*)x,
+                         (const bf16*)gate, gate_ld, (bf16*)out, out_ld, total, heads, vdim, factor);
+  return PKV_ERR_DTYPE;
 }

@@ -27,7 +27,7 @@ from paged_kv_serving_b200.engine.batch import BatchEntry, ExecutionBatch
 from paged_kv_serving_b200.engine.sequence import TableSnapshot
 from paged_kv_serving_b200.models.decoder import DecoderModel
 from paged_kv_serving_b200.ops import arena, gemm, mixer_ops
-from paged_kv_serving_b200.parts.base import CacheBinding, GroupView, IntArena, StepContext
+from paged_kv_serving_b200.parts.base import CacheBinding, GroupView, IntArena, Normed, StepContext
 
 __all__ = ["CacheStorage", "ModelRunner", "StepResult"]
 
@@ -136,7 +136,7 @@ class ModelRunner:
         self.num_blocks = num_blocks
         self.block_size = block_size
         self.order = model.layout.resolved_order()
-        self._readds_input = any(call.add_input for call in self.order)
+        self._readds_input = any(call.add_input or call.enter_pass is not None for call in self.order)
         self.groups, self.state_entries = plan_groups(model.layout.cache_entries())
         self.num_state_slots = max_running_seqs if self.state_entries else 0
         self.storage = CacheStorage(self.groups, self.state_entries, num_blocks=num_blocks, block_size=block_size,
@@ -166,7 +166,8 @@ class ModelRunner:
         self.steps_run = 0
         self.use_graphs = use_graphs
         layout = model.layout
-        self._graph_safe = all(part.graph_safe for part in (*layout.blocks, layout.final_norm, layout.embedding, layout.head))
+        ends = [part for part in (layout.final_norm, layout.embedding, layout.head, layout.pass_input) if part is not None]
+        self._graph_safe = all(part.graph_safe for part in (*layout.blocks, *ends))
         self._graphs: dict[tuple[int, int], dict] = {}
         self._last_graph_step: tuple[ExecutionBatch, tuple[int, int]] | None = None
         self._ahead: dict | None = None
@@ -320,11 +321,18 @@ class ModelRunner:
             if call.add_input:
                 # (additions commute: an update still pending behind the block before is added by this block)
                 mixer_ops.residual_add(hidden, model_input)
+            if call.enter_pass is not None:
+                # a pass over a repeated span starts: the stream (with what is still pending) and the model's
+                # input become the stream's new value
+                if isinstance(delta, Normed):
+                    raise ValueError("the stream was normalised for a block in front of which a pass starts")
+                model.layout.pass_input.forward(hidden, delta, model_input, call.enter_pass)
+                delta = None
             # the block may carry the next block's first norm in the tail of its last kernel; the
             # last block hands on its plain update (the final norm takes only the wanted rows)
             following = blocks[self.order[i + 1].layer] if i + 1 < len(self.order) else None
             if following is not None and getattr(following, "first_norm", None) is not None \
-                    and not self.order[i + 1].add_input:
+                    and not self.order[i + 1].add_input and self.order[i + 1].enter_pass is None:
                 delta = blocks[call.layer].forward(hidden, delta, ctx, binding, next_norm=following.first_norm)
             else:
                 delta = blocks[call.layer].forward(hidden, delta, ctx, binding)

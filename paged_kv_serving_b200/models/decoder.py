@@ -8,7 +8,7 @@ import torch
 
 from paged_kv_serving_b200.config import registry
 from paged_kv_serving_b200.config.model_config import ModelConfig
-from paged_kv_serving_b200.models.layout import ModelLayout
+from paged_kv_serving_b200.models.layout import ModelLayout, layout_for
 from paged_kv_serving_b200.weights import loader, random_init
 
 __all__ = ["DecoderModel", "TORCH_DTYPES"]
@@ -38,7 +38,7 @@ class DecoderModel:
     def from_tensors(cls, config: ModelConfig, tensors: dict[str, torch.Tensor], dtype: str = "bfloat16",
                      device: str | torch.device = "cuda") -> "DecoderModel":
         """Build from a name -> tensor mapping (as read from safetensors, or drawn at random)."""
-        layout = registry.architecture(config.architecture).layout(config)
+        layout = layout_for(config, tensors)
         model = cls(config, layout, dtype, torch.device(device))
         specs = layout.tensor_specs()
         if layout.optional_names:

@@ -2,11 +2,11 @@
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 
 from paged_kv_serving_b200.parts.base import ParamSpec, Part
 
-__all__ = ["LayerCall", "ModelLayout", "collect_param_specs"]
+__all__ = ["LayerCall", "ModelLayout", "collect_param_specs", "layout_for"]
 
 
 @dataclass(frozen=True, slots=True)
@@ -25,6 +25,10 @@ class LayerCall:
     #: The model's input (the embedding part's output for the step's tokens) is added to the
     #: stream once more right before this call: the start of a repeated pass over a span of layers.
     add_input: bool = False
+    #: The number of the pass over a repeated span of layers that starts right before this call: the
+    #: layout's ``pass_input`` part gives the stream its new value from the stream and the model's input
+    #: (``None``: no pass starts here).
+    enter_pass: int | None = None
 
 
 @dataclass(slots=True)
@@ -54,6 +58,9 @@ class ModelLayout:
     head: Part | None = None
     #: Tensors a model folder may hold although the layout has no use for them (they are not loaded).
     optional_names: set = field(default_factory=set)
+    #: The part that runs in front of every layer call with ``enter_pass`` (``forward(hidden, pending,
+    #: model_input, pass number)`` gives the stream its new value in place); its tensors are named in ``names``.
+    pass_input: Part | None = None
 
     def __post_init__(self) -> None:
         from paged_kv_serving_b200.parts.io import LinearHead, TokenEmbedding
@@ -68,6 +75,9 @@ class ModelLayout:
             self.head = LinearHead(self.vocab_size, self.width, tied=tied)
             if self.head_name is not None:
                 self.names[self.head_name] = (self.head, "weight")
+
+        if self.pass_input is None and any(call.enter_pass is not None for call in self.order):
+            raise ValueError("a layer call starts a pass but the layout has no part for it")
 
     def tensor_specs(self) -> dict[str, ParamSpec]:
         return {name: part.param_specs()[local] for name, (part, local) in self.names.items()}
@@ -111,15 +121,14 @@ class ModelLayout:
             if not 0 <= call.layer < len(self.blocks):
                 raise ValueError(f"layer call names layer {call.layer}, the model has {len(self.blocks)}")
             if call.cache is None and self.blocks[call.layer].cache_request() is not None:
-                call = LayerCall(call.layer, next_free, call.write, add_input=call.add_input)
+                call = replace(call, cache=next_free)
                 next_free += 1
             out.append(call)
         # the further states of every call come after all primary entries, one entry per call and name
         for i, call in enumerate(out):
             names = sorted(self.blocks[call.layer].state_requests())
             if names and not call.extra:
-                out[i] = LayerCall(call.layer, call.cache, call.write,
-                                   tuple((name, next_free + k) for k, name in enumerate(names)), call.add_input)
+                out[i] = replace(call, extra=tuple((name, next_free + k) for k, name in enumerate(names)))
                 next_free += len(names)
         return out
 
@@ -131,3 +140,14 @@ def collect_param_specs(prefix: str, part: Part, into: dict[str, tuple[Part, str
         into[prefix + local] = (part, local)
     for child_name, child in part.sub_parts().items():
         collect_param_specs(f"{prefix}{child_name}.", child, into)
+
+
+def layout_for(config, tensors: dict | None = None) -> ModelLayout:
+    """The layout of the architecture ``config`` names. An architecture some of whose sizes only a tensor's shape gives
+    (its class says ``sizes_from_tensors``) also gets the shapes of ``tensors`` (name -> tensor) where there are any."""
+    from paged_kv_serving_b200.config import registry
+
+    builder = registry.architecture(config.architecture)
+    if tensors is not None and getattr(builder, "sizes_from_tensors", False):
+        return builder.layout(config, tensor_shapes={name: tuple(t.shape) for name, t in tensors.items()})
+    return builder.layout(config)

@@ -1,6 +1,6 @@
 """Bindings of the kernels in ``csrc/pointwise.cu``, ``csrc/conv_state.cu``, ``csrc/mlstm.cu``,
-``csrc/selective_scan.cu``, ``csrc/latent_attention.cu``, ``csrc/attention_sink.cu``, ``csrc/layernorm.cu`` and
-``csrc/lightning.cu``: what mixers
+``csrc/selective_scan.cu``, ``csrc/latent_attention.cu``, ``csrc/attention_sink.cu``, ``csrc/layernorm.cu``,
+``csrc/lightning.cu`` and ``csrc/linear_attention.cu``: what mixers
 with a state of their own, a cached latent, a window that keeps the first tokens, routed experts
 and per-token side inputs need beside the kernels bound in ``ops/__init__.py``.
 The same conventions hold: CUDA tensors only, launches on torch's current stream, a refused
@@ -21,7 +21,8 @@ __all__ = ["ACTIVATIONS", "act_times_table", "bias_act", "conv_residual", "exper
            "latent_attention_mma", "latent_mma_rows_per_block", "latent_mma_supports", "latent_prepare",
            "latent_rows_per_block", "mlstm", "residual_add", "route_top", "token_side", "attention_sink",
            "attention_sink_mma", "attention_sink_mma_rows", "attention_sink_mma_supports", "attention_sink_rows_per_block", "qkv_prepare", "selective_scan",
-           "layer_norm_step", "lightning", "lightning_chunk", "softcap", "token_shift"]
+           "layer_norm_step", "lightning", "lightning_chunk", "softcap", "token_shift", "route_scored", "gated_bias_act",
+           "pair_rows", "assign_bias", "combine_pair", "head_gate", "linear_attention", "linear_attention_chunk"]
 
 #: activation names of ``bias_act`` / ``act_times_table`` / ``expert_act``
 ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "relu_squared": 3, "sigmoid": 4, "silu": 5}
@@ -426,7 +427,7 @@ def qkv_prepare(qkv: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor |
                 n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int, status: torch.Tensor,
                 v_other: torch.Tensor | None = None, blend: torch.Tensor | None = None,
                 keep_values: torch.Tensor | None = None, q_weight: torch.Tensor | None = None,
-                k_weight: torch.Tensor | None = None) -> None:
+                k_weight: torch.Tensor | None = None, bias: torch.Tensor | None = None, joint_norm: bool = False) -> None:
     """In ``qkv [tokens, >= H dim + G dim + G vdim]`` (columns ``[Q | K | V]``): rotate the first
     ``rot_dims`` coordinates of every query and key head (``freq [rot_dims / 2]`` float32 angular
     frequencies, cos and sin times ``rot_factor``), divide those heads by their root mean square
@@ -435,7 +436,10 @@ def qkv_prepare(qkv: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor |
     page_size, dim]`` at ``slots``; blend the values with ``v_other [tokens, G vdim]`` (weight
     ``blend``, a float32 tensor of one element: ``(1 - blend) v + blend v_other``) and write them
     into ``v_pool [pages, G, page_size, vdim]``. ``keep_values [tokens, G vdim]`` (type of ``qkv``)
-    also receives the values as they are cached."""
+    also receives the values as they are cached. ``bias`` (float32, one element per column ``[Q | K | V]``)
+    is added to the columns first. ``joint_norm``: in place of the norm per head, all query columns of a
+    token are divided by their joint root mean square and multiplied by ``q_weight [H dim]`` (the key
+    columns likewise, ``k_weight [G dim]``) before the rotation."""
     _need(qkv, None, "qkv"); _need(positions, torch.int32, "positions"); _need(k_pool, None, "k_pool")
     _need(v_pool, k_pool.dtype, "v_pool")
     tokens, ld = qkv.shape
@@ -457,17 +461,23 @@ def qkv_prepare(qkv: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor |
         if kept.shape != (tokens, n_kv * vdim):
             raise ValueError("keep_values must be [tokens, G * vdim]")
     pool_slots = k_pool.numel() // (n_kv * dim)
-    for name, t in (("q_weight", q_weight), ("k_weight", k_weight)):
+    for name, t, heads_of in (("q_weight", q_weight, n_heads), ("k_weight", k_weight, n_kv)):
         if t is not None:
             _need(t, torch.float32, name)
-            if t.numel() != dim:
-                raise ValueError(f"{name} needs one element per coordinate of a head")
+            if t.numel() != (heads_of * dim if joint_norm else dim):
+                raise ValueError(f"{name} needs one element per coordinate of a head (per column with a joint norm)")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() < (n_heads + n_kv) * dim + n_kv * vdim:
+            raise ValueError("bias needs one element per query, key and value column")
+    if joint_norm and not unit_norm:
+        raise ValueError("a joint norm is a norm")
     fn = _fn("attention_sink", "pkv_qkv_prepare",
-             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p, c_int,
+             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int,
               c_void_p, c_void_p])
     _check(fn(_ptr(qkv), dtype_code(qkv.dtype), ld, _ptr(positions), _ptr(freq), int(rot_dims), float(rot_factor), float(eps),
-              int(bool(unit_norm)), _ptr(q_weight), _ptr(k_weight), _ptr(v_other), ld_other, _ptr(blend), _ptr(kept), _ptr(k_pool), _ptr(v_pool),
+              (2 if joint_norm else 1) if unit_norm else 0, _ptr(q_weight), _ptr(k_weight), _ptr(bias), _ptr(v_other), ld_other, _ptr(blend), _ptr(kept), _ptr(k_pool), _ptr(v_pool),
               dtype_code(k_pool.dtype), _ptr(slots), pool_slots, tokens, n_heads, n_kv, dim, vdim, page_size, _ptr(status),
               _stream()), "qkv_prepare")
 
@@ -697,3 +707,205 @@ def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
     fn = _fn("pointwise", "pkv_softcap", [c_void_p, c_longlong, c_float, c_void_p])
     _check(fn(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
     return x
+
+
+def route_scored(logits: torch.Tensor, experts: int, top: int, correction: torch.Tensor | None = None, groups: int = 1,
+                 keep: int = 1, scale: float = 1.0) -> torch.Tensor:
+    """Router weights ``[tokens, experts]`` (float32) from sigmoid scores: an expert is chosen by ``sigmoid(logit) +
+    correction`` (the choice score), weighted by ``sigmoid(logit)`` alone. The experts form ``groups`` equal groups of
+    neighbours; a group's score is the sum of its two largest choice scores, and only experts of the ``keep`` best
+    groups can be chosen. The weights of the ``top`` chosen experts are their scores over the sum of those scores (plus
+    ``1e-20``) times ``scale``; every other weight is zero. ``logits [tokens, >= experts]`` float32."""
+    _need(logits, torch.float32, "logits")
+    tokens, ld = logits.shape
+    if correction is not None:
+        _need(correction, torch.float32, "correction")
+        if correction.numel() != experts:
+            raise ValueError("the router's correction needs one element per expert")
+    out = _empty((tokens, experts), torch.float32, logits.device)
+    fn = _fn("pointwise", "pkv_route_scored",
+             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(logits), ld, _ptr(correction), _ptr(out), tokens, experts, top, int(groups), int(keep), float(scale),
+              _stream()), "route_scored")
+    return out
+
+
+def gated_bias_act(gate_up: torch.Tensor, up_at: int, n: int, gate_bias: torch.Tensor | None, up_bias: torch.Tensor | None,
+                   act: str) -> torch.Tensor:
+    """``act(gate + gate_bias) * (up + up_bias)`` ``[tokens, n]`` for rows that hold the ``n`` gate columns and, ``up_at``
+    columns further on, the up columns; the biases are float32 ``[n]`` or none."""
+    _need(gate_up, None, "gate_up")
+    tokens, ld = gate_up.shape
+    for name, t in (("gate_bias", gate_bias), ("up_bias", up_bias)):
+        if t is not None:
+            _need(t, torch.float32, name)
+            if t.numel() != n:
+                raise ValueError(f"{name} needs one element per column")
+    if up_at < n or ld < up_at + n:
+        raise ValueError("gated_bias_act: sizes do not fit")
+    out = _empty((tokens, n), gate_up.dtype, gate_up.device)
+    fn = _fn("pointwise", "pkv_gated_bias_act", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(gate_up), dtype_code(gate_up.dtype), ld, int(up_at), _ptr(gate_bias), _ptr(up_bias), _ptr(out), tokens, n,
+              ACTIVATIONS[act], _stream()), "gated_bias_act")
+    return out
+
+
+def pair_rows(hidden: torch.Tensor, delta: torch.Tensor | None, other: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``hidden += delta`` in place (with ``delta``), then ``[hidden | other]`` row by row in ``out_dtype``: the float32
+    stream beside a second float32 matrix of its shape, as the operand of one product, ``[tokens, 2 width]``."""
+    _need(hidden, torch.float32, "hidden"); _need(other, torch.float32, "other")
+    if other.shape != hidden.shape:
+        raise ValueError("the two matrices differ in shape")
+    if delta is not None:
+        _need(delta, None, "delta")
+        if delta.shape != hidden.shape:
+            raise ValueError("delta and hidden differ in shape")
+    rows, cols = hidden.shape
+    out = _empty((rows, 2 * cols), out_dtype, hidden.device)
+    fn = _fn("pointwise", "pkv_pair_rows", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p])
+    _check(fn(_ptr(hidden), _ptr(delta), dtype_code(delta.dtype) if delta is not None else 0, _ptr(other), _ptr(out),
+              dtype_code(out_dtype), rows, cols, _stream()), "pair_rows")
+    return out
+
+
+def assign_bias(hidden: torch.Tensor, value: torch.Tensor, bias: torch.Tensor | None) -> None:
+    """``hidden = value + bias`` (all float32; ``bias [width]`` or none): the stream takes a new value in place."""
+    _need(hidden, torch.float32, "hidden"); _need(value, torch.float32, "value")
+    if value.shape != hidden.shape:
+        raise ValueError("value and hidden differ in shape")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != hidden.shape[1]:
+            raise ValueError("bias does not fit the stream's width")
+    fn = _fn("pointwise", "pkv_assign_bias", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p])
+    _check(fn(_ptr(hidden), _ptr(value), _ptr(bias), hidden.shape[0], hidden.shape[1], _stream()), "assign_bias")
+
+
+def combine_pair(a: torch.Tensor, b: torch.Tensor, factor_a: float, factor_b: float,
+                 norm_weights: tuple[torch.Tensor, torch.Tensor] | None = None, eps: float = 1e-6) -> torch.Tensor:
+    """One update from two float32 updates of the same shape: ``factor_a * a + factor_b * b``, or, with ``norm_weights =
+    (wa, wb)`` (float32 ``[width]``), each first divided by its root mean square over the row (``eps`` inside the root)
+    and multiplied by its weight. Float32 ``[tokens, width]``."""
+    _need(a, torch.float32, "a"); _need(b, torch.float32, "b")
+    if a.shape != b.shape:
+        raise ValueError("the two updates differ in shape")
+    wa = wb = None
+    if norm_weights is not None:
+        wa, wb = norm_weights
+        _need(wa, torch.float32, "norm weight"); _need(wb, torch.float32, "norm weight")
+        if wa.numel() != a.shape[1] or wb.numel() != a.shape[1]:
+            raise ValueError("a norm's weight does not fit the width")
+    out = _empty(tuple(a.shape), torch.float32, a.device)
+    fn = _fn("pointwise", "pkv_combine_pair", [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_void_p, c_int,
+                                                c_int, c_void_p])
+    _check(fn(_ptr(a), _ptr(b), _ptr(wa), _ptr(wb), float(factor_a), float(factor_b), float(eps), _ptr(out), a.shape[0], a.shape[1],
+              _stream()), "combine_pair")
+    return out
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor | None, heads: int, vdim: int, factor: float = 1.0,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x[t, h * vdim + j] * sigmoid(gate[t, h]) * factor`` for ``x [tokens, heads * vdim]``: in place, or written to
+    ``out`` (a view of the same type whose rows may have a stride); returns where the result lies. ``gate`` is a view
+    ``[tokens, heads]`` of the type of ``x`` whose rows may have a stride, or none (the factor alone)."""
+    _need(x, None, "x")
+    tokens = x.shape[0]
+    n = heads * vdim
+    if x.shape[1] != n:
+        raise ValueError("x must hold heads * vdim columns")
+    gate_ld = 0
+    if gate is not None:
+        if not gate.is_cuda or gate.dtype != x.dtype or gate.dim() != 2 or gate.shape != (tokens, heads) or gate.stride(1) != 1:
+            raise ValueError("gate must be a [tokens, heads] view of the type of x with unit inner stride")
+        gate_ld = gate.stride(0) if tokens > 1 else max(gate.stride(0), heads)
+    if out is None:
+        out = x
+    elif not out.is_cuda or out.dtype != x.dtype or out.dim() != 2 or out.shape != (tokens, n) or out.stride(1) != 1:
+        raise ValueError("out must be a [tokens, heads * vdim] view of the type of x with unit inner stride")
+    out_ld = out.stride(0) if tokens > 1 else max(out.stride(0), n)
+    fn = _fn("pointwise", "pkv_head_gate", [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(x), c_void_p(gate.data_ptr() if gate is not None else 0), dtype_code(x.dtype), gate_ld,
+              c_void_p(out.data_ptr()), out_ld, tokens, heads, vdim, float(factor), _stream()), "head_gate")
+    return out
+
+
+#: tokens of one entry up to which ``linear_attention`` walks them in a row, and its chunk sizes (as for ``lightning``)
+LINEAR_ATTENTION_IN_A_ROW = 128
+LINEAR_ATTENTION_CHUNK, LINEAR_ATTENTION_CHUNKS = 64, 64
+
+
+def linear_attention_chunk(tokens: int, seqs: int) -> int:
+    """Tokens per chunk for a step of ``tokens`` tokens in ``seqs`` entries: 0 when no entry can be longer than
+    ``LINEAR_ATTENTION_IN_A_ROW``, else ``LINEAR_ATTENTION_CHUNK`` or, for very long steps, a multiple of 16 that keeps
+    the working memory at about ``LINEAR_ATTENTION_CHUNKS`` states per head."""
+    if tokens - (seqs - 1) <= LINEAR_ATTENTION_IN_A_ROW:
+        return 0
+    return max(LINEAR_ATTENTION_CHUNK, -(-tokens // (LINEAR_ATTENTION_CHUNKS * 16)) * 16)
+
+
+def linear_attention(proj: torch.Tensor, offsets: dict[str, int], state: torch.Tensor, seq_starts: torch.Tensor,
+                     state_slots: torch.Tensor, heads: int, dim: int, vdim: int, out_dtype: torch.dtype, *,
+                     head_decay: torch.Tensor | None = None, decay_pre: torch.Tensor | None = None,
+                     decay_bias: torch.Tensor | None = None, inv_tau: float = 1.0,
+                     q_scale: float = 1.0, k_scale: float = 1.0, rot_dims: int = 0, freq: torch.Tensor | None = None,
+                     positions: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None, eps: float = 1e-6,
+                     out_factor: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Linear attention with a matrix state per head over a ragged batch: ``S_t = diag(a_t) S_(t-1) + k_t v_t^T``, ``o_t
+    = S_t^T q_t``. ``proj`` float32 ``[tokens, ld]`` holds q and k ``[heads, dim]``, v and the output gate's
+    pre-activation ``[heads, vdim]`` at ``offsets`` ("q", "k", "v", "g"). The decay is either ``head_decay`` (float32
+    ``[heads]``, one fixed number per head) or, with ``decay_pre`` (float32 ``[tokens, heads * dim]``, rows may have a
+    stride), ``sigmoid(decay_pre + decay_bias) ** inv_tau`` per token and key coordinate. Queries and keys are first
+    rotated in their first ``rot_dims`` coordinates (coordinate ``i`` with ``i + rot_dims / 2``, angle ``positions[t] *
+    freq[i]``), then multiplied by ``q_scale`` / ``k_scale``. ``state`` float32 ``[slots, heads, vdim, dim]`` is read and
+    brought up to date. Returns, per head, the outputs divided by their root mean square over ``vdim``, times
+    ``norm_weight`` (float32 ``[vdim]`` or none), the SiLU of the gate and ``out_factor``: ``[tokens, heads * vdim]`` in
+    ``out_dtype``, or written into ``out`` (a view of that shape whose rows may have a stride)."""
+    _need(proj, torch.float32, "proj"); _need(state, torch.float32, "state")
+    tokens, ld = proj.shape
+    if state.shape[1:] != (heads, vdim, dim):
+        raise ValueError("linear_attention: the state does not fit heads, dim and vdim")
+    a_ld = 0
+    if decay_pre is None:
+        _need(head_decay, torch.float32, "head_decay")
+        if head_decay.numel() != heads:
+            raise ValueError("one decay per head")
+    else:
+        if not decay_pre.is_cuda or decay_pre.dtype != torch.float32 or decay_pre.dim() != 2 or decay_pre.stride(1) != 1 \
+                or decay_pre.shape[0] != tokens or decay_pre.shape[1] < heads * dim:
+            raise ValueError("decay_pre must be float32 [tokens, >= heads * dim] with unit inner stride")
+        a_ld = decay_pre.stride(0) if tokens > 1 else max(decay_pre.stride(0), heads * dim)
+    if decay_bias is not None:
+        _need(decay_bias, torch.float32, "decay_bias")
+        if decay_bias.numel() != heads * dim:
+            raise ValueError("the decay's bias needs one element per head and key coordinate")
+    if norm_weight is not None:
+        _need(norm_weight, torch.float32, "norm_weight")
+        if norm_weight.numel() != vdim:
+            raise ValueError("the norm's weight needs one element per value coordinate")
+    if rot_dims:
+        _need(freq, torch.float32, "freq"); _need(positions, torch.int32, "positions")
+        if freq.numel() != rot_dims // 2:
+            raise ValueError("freq needs one element per rotated pair")
+    seqs = seq_starts.numel() - 1
+    n = heads * vdim
+    if out is None:
+        out = _empty((tokens, n), out_dtype, proj.device)
+    elif not out.is_cuda or out.dtype != out_dtype or out.dim() != 2 or out.shape != (tokens, n) or out.stride(1) != 1:
+        raise ValueError("out must be [tokens, heads * vdim] of out_dtype with unit inner stride")
+    out_ld = out.stride(0) if tokens > 1 else max(out.stride(0), n)
+    scratch = _empty((tokens, n), torch.float32, proj.device)
+    chunk = linear_attention_chunk(tokens, seqs)
+    chunk_state = _empty((tokens // chunk + seqs, heads, vdim, dim), torch.float32, proj.device) if chunk else None
+    chunk_decay = _empty((tokens // chunk + seqs, heads, dim), torch.float32, proj.device) if chunk and decay_pre is not None else None
+    fn = _fn("linear_attention", "pkv_linear_attention",
+             [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_float, c_float, c_int,
+              c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+              c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(proj), ld, offsets["q"], offsets["k"], offsets["v"], offsets["g"],
+              c_void_p(decay_pre.data_ptr() if decay_pre is not None else 0), a_ld, _ptr(decay_bias), float(inv_tau),
+              _ptr(head_decay), float(q_scale), float(k_scale), int(rot_dims), _ptr(freq), _ptr(positions), _ptr(norm_weight),
+              float(eps), float(out_factor), _ptr(state), _ptr(seq_starts), _ptr(state_slots), _ptr(scratch),
+              c_void_p(out.data_ptr()), dtype_code(out_dtype), out_ld, tokens, seqs, heads, dim, vdim, chunk,
+              _ptr(chunk_state), _ptr(chunk_decay), _stream()), "linear_attention")
+    ops.LAUNCHES["count"] += 3 if chunk else 1
+    return out

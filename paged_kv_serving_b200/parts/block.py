@@ -14,7 +14,8 @@ __all__ = ["ConvSideBlock", "PostNormBlock", "PreNormBlock", "SandwichBlock"]
 @register_part("block", "prenorm_residual")
 class PreNormBlock(Block):
     """Pre-norm residual arrangement: ``h += mixer(norm(h)); h += feed_forward(norm(h))``
-    (reference: src/paged_kv_serving/engine/model.py:283-287, src/paged_kv_serving/engine/runner.py:213-214).
+    (reference: src/paged_kv_serving/engine/model.py:283-287, src/paged_kv_serving/engine/runner.py:213-214);
+    a layer may have no feed-forward (and then no second norm).
 
     The hand-over between blocks (pending updates, ``Normed``) is the one ``parts.base.Block``
     describes: a block receives the previous block's output as a pending update and returns its
@@ -26,18 +27,23 @@ class PreNormBlock(Block):
         return all(child.graph_safe for child in self.sub_parts().values())
 
 
-    def __init__(self, mixer_norm: Part, mixer: Part, ff_norm: Part, feed_forward: Part) -> None:
+    def __init__(self, mixer_norm: Part, mixer: Part, ff_norm: Part | None = None, feed_forward: Part | None = None) -> None:
+        if (ff_norm is None) != (feed_forward is None):
+            raise ValueError("a feed-forward and its norm go together")
         self.mixer_norm = mixer_norm
         self.mixer = mixer
         self.ff_norm = ff_norm
         self.feed_forward = feed_forward
 
     def sub_parts(self) -> dict[str, Part]:
-        return {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "ff_norm": self.ff_norm,
-                "feed_forward": self.feed_forward}
+        parts = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "ff_norm": self.ff_norm, "feed_forward": self.feed_forward}
+        return {name: part for name, part in parts.items() if part is not None}
 
     def cache_request(self):
         return self.mixer.cache_request()
+
+    def state_requests(self):
+        return self.mixer.state_requests()
 
     def plan_step(self, ctx: StepContext, binding: CacheBinding | None) -> None:
         # only the children that plan anything (this runs for every layer of every step)
@@ -67,6 +73,9 @@ class PreNormBlock(Block):
             if isinstance(pending, Normed):
                 raise ValueError("the stream was normalised for another block than the one that runs next")
             normed = self.mixer_norm.add_norm(hidden, pending, ctx.dtype)
+        if self.feed_forward is None:
+            # a layer without a feed-forward: the mixer's update is what is pending behind the block
+            return self.mixer.forward(gemm.as_tensor(normed), ctx, binding)
         follow = getattr(self.ff_norm, "add_norm_of_linear", None)
         if self.mixer.fuses_last_linear and follow is not None:
             chain = self.mixer.chains_last_linear

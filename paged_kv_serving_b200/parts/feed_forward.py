@@ -9,7 +9,7 @@ from paged_kv_serving_b200.config.registry import register_part
 from paged_kv_serving_b200.ops import gemm
 from paged_kv_serving_b200.parts.base import ParamSpec, Part, StepContext
 
-__all__ = ["BiasedDense", "Dense", "GatedRoutedExperts", "RoutedExperts", "SwiGLU"]
+__all__ = ["BiasedDense", "Dense", "GatedDense", "GatedRoutedExperts", "RoutedExperts", "SwiGLU"]
 
 
 @register_part("feed_forward", "swiglu")
@@ -127,6 +127,47 @@ class Dense(Part):
         return gemm.linear(inner, self.down, out_dtype=torch.float32, few_rows_f32=True, chain=True)
 
 
+@register_part("feed_forward", "gated_dense")
+class GatedDense(Part):
+    """``W_down (act(W_gate x + b_gate) * (W_up x + b_up)) + b_down`` (``act`` the tanh form of GELU unless given;
+    ``bias=False``: no biases); weights ``[out, in]``. Gate and up are one product; the result is float32: what a norm
+    or the residual sum reads."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, inner: int, activation: str = "gelu_tanh", bias: bool = True) -> None:
+        self.width, self.inner, self.activation, self.bias = int(width), int(inner), activation, bool(bias)
+        self.up_at = -(-self.inner // 8) * 8           # the up columns start on a 16-byte boundary
+        self.gate_b = self.up_b = self.down_b = None
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        specs = {"gate": ParamSpec((self.inner, self.width)), "up": ParamSpec((self.inner, self.width)),
+                 "down": ParamSpec((self.width, self.inner))}
+        if self.bias:
+            specs.update({"gate_b": ParamSpec((self.inner,), "vector", init=(0.0, 0.1)),
+                          "up_b": ParamSpec((self.inner,), "vector", init=(0.0, 0.1)),
+                          "down_b": ParamSpec((self.width,), "vector", init=(0.0, 0.1))})
+        return specs
+
+    def load(self, params: dict[str, torch.Tensor]) -> None:
+        gate = params["gate"]
+        gate_up = torch.zeros((2 * self.up_at, self.width), dtype=gate.dtype, device=gate.device)
+        gate_up[:self.inner] = gate
+        gate_up[self.up_at:self.up_at + self.inner] = params["up"]
+        self.gate_up = gate_up                                              # [gate (padded) | up (padded), width]
+        self.down = params["down"].contiguous()
+        for name in ("gate_b", "up_b", "down_b"):
+            setattr(self, name, params[name].contiguous() if name in params else None)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        from paged_kv_serving_b200.ops import mixer_ops
+
+        gate_up = gemm.linear(x, self.gate_up, chain=True)
+        inner = mixer_ops.gated_bias_act(gate_up, self.up_at, self.inner, self.gate_b, self.up_b, self.activation)
+        out = gemm.linear(inner, self.down, out_dtype=torch.float32, few_rows_f32=True, chain=True)
+        return mixer_ops.bias_act(out, self.down_b, "none") if self.down_b is not None else out
+
+
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts(Part):
     """A mixture of small feed-forward experts ``W_down act(W_up x)`` without biases (``act`` the
@@ -205,14 +246,30 @@ class GatedRoutedExperts(Part):
     column's expert (exact zeros for an expert the token does not use), one product over the
     stacked down-projections, whose result stays float32. Nothing depends on values read back to
     the host, so decode steps can be captured.
+
+    ``scoring="sigmoid"`` is another router: an expert's score is ``sigmoid(logit)`` (no bias on the logits); experts
+    are chosen by score plus the tensor ``correction [experts]`` and weighted by the score alone; the experts form
+    ``groups`` equal groups of neighbours, a group's score is the sum of its two largest choice scores, and only experts
+    of the ``keep_groups`` best groups can be chosen; the chosen scores are divided by their sum (plus ``1e-20``) and
+    multiplied by ``weight_scale``.
     """
 
     graph_safe = True
 
     def __init__(self, width: int, experts: int, top: int, inner: int, shared_inner: int = 0, activation: str = "silu",
-                 router_bias: bool = True, renormalise: bool = True) -> None:
+                 router_bias: bool = True, renormalise: bool = True, scoring: str = "softmax", groups: int = 1,
+                 keep_groups: int = 1, weight_scale: float = 1.0) -> None:
         if not 1 <= top <= experts:
             raise ValueError("top must be between 1 and the number of experts")
+        if scoring not in ("softmax", "sigmoid"):
+            raise ValueError("scoring is 'softmax' or 'sigmoid'")
+        if scoring == "sigmoid":
+            if groups < 1 or groups > 64 or experts % groups or not 1 <= keep_groups <= groups:
+                raise ValueError("the experts form up to 64 equal groups, of which at least one and at most all are kept")
+            if top > experts // groups * keep_groups:
+                raise ValueError("more experts to choose than the kept groups hold")
+            router_bias = False
+        self.scoring, self.groups, self.keep_groups, self.weight_scale = scoring, int(groups), int(keep_groups), float(weight_scale)
         self.width, self.experts, self.top, self.inner = int(width), int(experts), int(top), int(inner)
         self.shared_inner, self.activation = int(shared_inner), activation
         self.router_bias, self.renormalise = bool(router_bias), bool(renormalise)
@@ -223,6 +280,8 @@ class GatedRoutedExperts(Part):
         specs = {"router": ParamSpec((self.experts, self.width))}
         if self.router_bias:
             specs["router_b"] = ParamSpec((self.experts,), "vector", init=(0.0, 0.1))
+        if self.scoring == "sigmoid":
+            specs["correction"] = ParamSpec((self.experts,), "vector", init=(0.0, 0.1))
         names = [f"e{e}" for e in range(self.experts)]
         for name in names:
             specs[f"{name}_gate"] = ParamSpec((self.inner, self.width))
@@ -247,12 +306,17 @@ class GatedRoutedExperts(Part):
         router[:self.experts] = first
         self.router = router
         self.router_b = params["router_b"].contiguous() if self.router_bias else None
+        self.correction = params["correction"].contiguous() if self.scoring == "sigmoid" else None
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         from paged_kv_serving_b200.ops import mixer_ops
 
         logits = gemm.linear(x, self.router, out_dtype=torch.float32, few_rows_f32=True, chain=True)       # [tokens, experts (padded)]
-        weights = mixer_ops.route_top(logits, self.experts, self.top, bias=self.router_b, renormalise=self.renormalise)
+        if self.scoring == "sigmoid":
+            weights = mixer_ops.route_scored(logits, self.experts, self.top, self.correction, self.groups, self.keep_groups,
+                                             self.weight_scale)
+        else:
+            weights = mixer_ops.route_top(logits, self.experts, self.top, bias=self.router_b, renormalise=self.renormalise)
         gate_up = gemm.linear(x, self.gate_up, chain=True)
         inner = mixer_ops.expert_gated_act(gate_up, self.up_at, weights, self.experts, self.inner, self.shared_inner,
                                            self.activation)

@@ -9,7 +9,7 @@ from paged_kv_serving_b200.config.registry import register_part
 from paged_kv_serving_b200.ops import gemm
 from paged_kv_serving_b200.parts.base import ParamSpec, Part, StepContext
 
-__all__ = ["LinearHead", "TokenEmbedding"]
+__all__ = ["LinearHead", "PassInput", "TokenEmbedding"]
 
 
 @register_part("embedding", "token_embedding")
@@ -76,3 +76,39 @@ class LinearHead(Part):
 
             mixer_ops.softcap(logits, self.softcap)
         return logits
+
+
+@register_part("embedding", "pass_input")
+class PassInput(Part):
+    """What stands in front of each pass over a span of layers that runs several times: the stream ``x`` is replaced by
+    ``W [x; x0] + step[t]``, with ``x0`` the model's input (the embedding part's output for the step's tokens), ``W
+    [width, 2 width]`` (tensor ``mix``, the columns of ``x`` first) and ``step [passes, width]``, ``t`` the number of the
+    pass. ``forward(hidden, pending, model_input, t)`` adds a pending update to the stream first, then gives the stream
+    its new value in place. The product takes operands in the compute type and keeps its float32 result, to which the
+    step vector is added in float32."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, passes: int) -> None:
+        if width < 1 or passes < 1:
+            raise ValueError("width and passes must be >= 1")
+        self.width, self.passes = int(width), int(passes)
+        self.mix: torch.Tensor | None = None
+        self.step: torch.Tensor | None = None
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        return {"mix": ParamSpec((self.width, 2 * self.width)),
+                "step": ParamSpec((self.passes, self.width), "vector", init=(0.0, 0.1))}
+
+    def load(self, params: dict[str, torch.Tensor]) -> None:
+        self.mix = params["mix"].contiguous()
+        self.step = params["step"].contiguous()
+
+    def forward(self, hidden: torch.Tensor, pending: torch.Tensor | None, model_input: torch.Tensor, number: int) -> None:
+        from paged_kv_serving_b200.ops import mixer_ops
+
+        if not 0 <= number < self.passes:
+            raise ValueError(f"pass {number} of {self.passes}")
+        both = mixer_ops.pair_rows(hidden, pending, model_input, self.mix.dtype)
+        mixed = gemm.linear(both, self.mix, out_dtype=torch.float32, few_rows_f32=True, chain=True)
+        mixer_ops.assign_bias(hidden, mixed, self.step[number])

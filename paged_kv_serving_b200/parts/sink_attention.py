@@ -36,6 +36,14 @@ class SinkWindowAttention(Part):
       ``r1``, ``r2`` ``[H]``);
     * ``window`` and ``keep_first``: position ``i`` sees ``j <= i`` when ``i - j < window`` or ``j <
       keep_first`` (``window=None``: all earlier positions); kept tokens keep their own positions;
+    * ``bias``: the three projections have biases (tensors ``q_b``, ``k_b``, ``v_b``), added before anything else;
+    * ``joint_norm`` (with ``unit_norm``): in place of the norm per head, all query columns of a token are divided by
+      their joint root mean square and multiplied by ``q_norm [H dim]``, the key columns by theirs and ``k_norm [G
+      dim]``, before the rotation;
+    * ``pairing``: the rotation pairs coordinate ``i`` with ``i + rot / 2`` ("halves") or ``2i`` with ``2i + 1``
+      ("interleaved"; the rows of ``W_q`` and ``W_k``, their biases and norm weights are reordered at load, evens in
+      front of odds, which turns one into the other without changing any score);
+    * ``head_gate``: head ``h``'s output is multiplied by ``sigmoid(W_g x)_h`` (tensor ``g [H, width]``) before ``W_o``;
     * ``value_share``: ``"source"`` leaves this layer's values of the step's tokens in the step's
       scratch under ``share_key``; ``"blend"`` replaces ``v`` by ``(1 - lambda) v + lambda v_source``
       with ``lambda`` the tensor ``vmix`` and ``v_source`` what the source layer left for the same
@@ -67,7 +75,8 @@ class SinkWindowAttention(Part):
                  rotary: ScaledRotaryFrequencies | None = None, unit_norm: bool = True, eps: float = 1e-6,
                  softcap: float = 0.0, window: int | None = None, keep_first: int = 0, value_share: str | None = None,
                  share_key: str = "sink_attention/shared_values", norm_weights: bool = False,
-                 head_temperature: bool = False, distance_bias: bool = False) -> None:
+                 head_temperature: bool = False, distance_bias: bool = False, bias: bool = False, joint_norm: bool = False,
+                 pairing: str = "halves", head_gate: bool = False) -> None:
         if n_heads < 1 or n_kv_heads < 1 or n_heads % n_kv_heads:
             raise ValueError("n_heads must be a multiple of n_kv_heads")
         if window is not None and window < 1:
@@ -87,10 +96,16 @@ class SinkWindowAttention(Part):
         if norm_weights and not unit_norm:
             raise ValueError("norm weights belong to the unit norm of queries and keys")
         self.norm_weights, self.head_temperature, self.distance_bias = bool(norm_weights), bool(head_temperature), bool(distance_bias)
-        self.q_norm = self.k_norm = self.temp = self.r1 = self.r2 = None
+        if joint_norm and not (unit_norm and norm_weights):
+            raise ValueError("the joint norm of queries and keys is a unit norm with weights")
+        if pairing not in ("halves", "interleaved"):
+            raise ValueError("pairing is 'halves' or 'interleaved'")
+        self.bias, self.joint_norm, self.pairing, self.head_gate = bool(bias), bool(joint_norm), pairing, bool(head_gate)
+        self.q_norm = self.k_norm = self.temp = self.r1 = self.r2 = self.qkv_bias = None
         self.q_cols = self.n_heads * self.dim
         self.kv_cols = self.n_kv_heads * (self.dim + self.vdim)
-        self.fused_rows = _round_up(self.q_cols + self.kv_cols, 8)
+        self.gate_at = self.q_cols + self.kv_cols          # the gates' columns in the fused projection
+        self.fused_rows = _round_up(self.gate_at + (self.n_heads if self.head_gate else 0), 8)
         self._fast_ok: dict = {}
 
     @property
@@ -105,8 +120,14 @@ class SinkWindowAttention(Part):
         if self.value_share is not None:
             specs["vmix"] = ParamSpec((), "vector", init=(0.5, 0.0))
         if self.norm_weights:
-            specs["q_norm"] = ParamSpec((self.dim,), "vector")
-            specs["k_norm"] = ParamSpec((self.dim,), "vector")
+            specs["q_norm"] = ParamSpec((self.q_cols if self.joint_norm else self.dim,), "vector")
+            specs["k_norm"] = ParamSpec((self.n_kv_heads * self.dim if self.joint_norm else self.dim,), "vector")
+        if self.bias:
+            specs["q_b"] = ParamSpec((self.q_cols,), "vector", init=(0.0, 0.1))
+            specs["k_b"] = ParamSpec((self.n_kv_heads * self.dim,), "vector", init=(0.0, 0.1))
+            specs["v_b"] = ParamSpec((self.n_kv_heads * self.vdim,), "vector", init=(0.0, 0.1))
+        if self.head_gate:
+            specs["g"] = ParamSpec((self.n_heads, self.width))
         if self.head_temperature:
             specs["temp"] = ParamSpec((self.n_heads,), "vector", init=(1.0, 0.2))
         if self.distance_bias:
@@ -114,19 +135,44 @@ class SinkWindowAttention(Part):
             specs["r2"] = ParamSpec((self.n_heads,), "vector", init=(0.5, 0.2))
         return specs
 
+    def _halves_order(self, heads: int) -> torch.Tensor | None:
+        """For an interleaved rotation: the order of the ``heads * dim`` rows (or elements) that puts, inside every
+        head, the even rotated coordinates in front of the odd ones; ``None`` when nothing moves."""
+        rot = self.rotary.dims if self.rotary is not None else 0
+        if self.pairing != "interleaved" or not rot:
+            return None
+        inside = list(range(0, rot, 2)) + list(range(1, rot, 2)) + list(range(rot, self.dim))
+        return torch.tensor([h * self.dim + d for h in range(heads) for d in inside], dtype=torch.long)
+
     def load(self, params: dict[str, torch.Tensor]) -> None:
         q = params["q"]
+        params = dict(params)
+        for heads, names in ((self.n_heads, ("q", "q_b", "q_norm")), (self.n_kv_heads, ("k", "k_b", "k_norm"))):
+            order = self._halves_order(heads)
+            if order is None:
+                continue
+            for name in names:
+                if name not in params:
+                    continue
+                t = params[name]
+                if name.endswith("_norm") and not self.joint_norm:
+                    t = t[order[:self.dim].to(t.device)]            # one weight per coordinate of a head
+                else:
+                    t = t[order.to(t.device)]
+                params[name] = t
         fused = torch.zeros((self.fused_rows, self.width), dtype=q.dtype, device=q.device)
         at = 0
-        for name in ("q", "k", "v"):
+        for name in ("q", "k", "v") + (("g",) if self.head_gate else ()):
             rows = params[name].shape[0]
             fused[at:at + rows] = params[name]
             at += rows
-        self.qkv = fused                                   # [H dim + G dim + G vdim (padded), width]
+        self.qkv = fused                                   # [H dim + G dim + G vdim (+ H gates) (padded), width]
         self.o = params["o"].contiguous()
         self.blend = params["vmix"].reshape(1).contiguous() if "vmix" in params else None
         for name in ("q_norm", "k_norm", "temp", "r1", "r2"):
             setattr(self, name, params[name].contiguous() if name in params else None)
+        if self.bias:
+            self.qkv_bias = torch.cat([params["q_b"], params["k_b"], params["v_b"]]).to(torch.float32).contiguous()
 
     def cache_request(self) -> PagedKVRequest:
         return PagedKVRequest(self.n_kv_heads, self.dim, self.window, value_dim=self.vdim,
@@ -348,6 +394,22 @@ class SinkWindowAttention(Part):
         return out
 
     def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding) -> torch.Tensor:
+        attended, chain = self._inner(x, ctx, binding, None, 1.0)
+        # the float32 result of the last product goes to a norm
+        return gemm.linear(attended, self.o, out_dtype=torch.float32, few_rows_f32=True, chain=chain)
+
+    @property
+    def last_weight(self) -> torch.Tensor:
+        return self.o
+
+    def inner(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding, out: torch.Tensor | None = None,
+              factor: float = 1.0) -> torch.Tensor:
+        """Everything in front of ``W_o``: the heads' (gated) outputs times ``factor``, ``[tokens, H vdim]`` in the compute
+        type, written to ``out`` where one is given (a view whose rows may have a stride)."""
+        return self._inner(x, ctx, binding, out, factor)[0]
+
+    def _inner(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding, out: torch.Tensor | None,
+               factor: float) -> tuple[torch.Tensor, bool]:
         group = ctx.groups[binding.group]
         k_pool, v_pool = group.k_pool[binding.index], group.v_pool[binding.index]
         slots = ctx.ints(group.slots_name) if binding.write else None
@@ -369,24 +431,31 @@ class SinkWindowAttention(Part):
             rotary.dims if rotary else 0, rotary.amplitude if rotary else 1.0, self.eps, self.unit_norm, k_pool, v_pool,
             slots, self.n_heads, self.n_kv_heads, self.dim, self.vdim, group.page_size, ctx.status,
             v_other=other, blend=self.blend if other is not None else None, keep_values=shared,
-            q_weight=self.q_norm, k_weight=self.k_norm)
+            q_weight=self.q_norm, k_weight=self.k_norm, bias=self.qkv_bias, joint_norm=self.joint_norm)
+        attended, chain = self.attend(qkv, ctx, group, k_pool, v_pool)
+        if self.head_gate or out is not None or factor != 1.0:
+            gate = qkv[:, self.gate_at:self.gate_at + self.n_heads] if self.head_gate else None
+            attended = mixer_ops.head_gate(attended, gate, self.n_heads, self.vdim, factor, out=out)
+        return attended, chain
+
+    def attend(self, qkv: torch.Tensor, ctx: StepContext, group, k_pool, v_pool) -> tuple[torch.Tensor, bool]:
+        """The attention itself over prepared queries and the cache: ``[tokens, H vdim]`` in the compute type, and
+        whether a product behind it may be chained to the kernel that made it."""
         bias = (self.r1, self.r2) if self.distance_bias else None
         if self._fast(ctx, group.page_size):
-            return gemm.linear(self._attend_fast(qkv, ctx, group, k_pool, v_pool), self.o, out_dtype=torch.float32, few_rows_f32=True)
+            return self._attend_fast(qkv, ctx, group, k_pool, v_pool), False
         if self._shaped_split(ctx, group.page_size):
-            return gemm.linear(self._attend_shaped(qkv, ctx, group, k_pool, v_pool, bias), self.o, out_dtype=torch.float32,
-                               few_rows_f32=True)
+            return self._attend_shaped(qkv, ctx, group, k_pool, v_pool, bias), False
         if self._mma(ctx):
             attended = mixer_ops.attention_sink_mma(
                 qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
                 ctx.ints(self._mma_names()[0]), ctx.ints(self._mma_names()[1]), self.n_heads, self.n_kv_heads,
                 self.dim, self.vdim, group.page_size, self.window or 0, self.keep_first, self.scale, self.softcap, ctx.status,
                 num_splits=self._mma_splits(ctx), head_scale=self.temp, distance_bias=bias)
-            return gemm.linear(attended, self.o, out_dtype=torch.float32, few_rows_f32=True, chain=True)
+            return attended, True
         seq_name, row_name = self._work_names()
         attended = mixer_ops.attention_sink(
             qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
             ctx.ints(seq_name), ctx.ints(row_name), self.n_heads, self.n_kv_heads, self.dim, self.vdim, group.page_size,
             self.window or 0, self.keep_first, self.scale, self.softcap, ctx.status, head_scale=self.temp, distance_bias=bias)
-        # the float32 result of the last product goes to a norm
-        return gemm.linear(attended, self.o, out_dtype=torch.float32, few_rows_f32=True, chain=True)
+        return attended, True

@@ -111,7 +111,9 @@ def cross_check_manifest(manifest: dict, config, tensors: dict[str, torch.Tensor
     if not same:
         raise manifest_module.ModelIntegrityError("the manifest's architecture is not the configuration in config.json")
     found = sum(int(t.numel()) for t in tensors.values())
-    declared = registry.architecture(config.architecture).layout(config).parameter_count()
+    from paged_kv_serving_b200.models.layout import layout_for
+
+    declared = layout_for(config, tensors).parameter_count()
     count = manifest.get("parameter_count")
     if count != found or count != declared:
         raise manifest_module.ModelIntegrityError(

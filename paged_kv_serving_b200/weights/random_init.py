@@ -89,7 +89,9 @@ def write_model_folder(folder: str | Path, config, tensors: dict[str, torch.Tens
     write_config(config, folder / CONFIG_FILE)
     save_file({name: tensor.detach().cpu().contiguous() for name, tensor in tensors.items()},
               str(folder / WEIGHTS_FILE))
-    layout = registry.architecture(config.architecture).layout(config)
+    from paged_kv_serving_b200.models.layout import layout_for
+
+    layout = layout_for(config, tensors)
     return manifest_module.write_manifest(folder, config.to_dict(), layout.parameter_count(),
                                           (CONFIG_FILE, WEIGHTS_FILE))
 
