@@ -6,8 +6,10 @@
 // them into the recurrence's inputs happens while a block stages them in shared memory:
 //   queries and keys: a rotation of the first `rot_dims` coordinates of a head by the token's
 //     position (coordinate i pairs with i + rot_dims / 2, angle = position * freq[i]), then a factor;
-//   the decay: a_t[d] = sigmoid(z_t[d] + bias[d]) ^ inv_tau, formed as exp(inv_tau * log sigmoid),
-//     or the head's fixed number.
+//   the decay: a_t[d] = sigmoid(z_t[d] + bias[d]) ^ inv_tau = exp(inv_tau * log sigmoid), staged as
+//     a_t[d] - 1 = expm1(inv_tau * log sigmoid) and applied as S + (a - 1) S: a decay close to 1 would
+//     round to 24 bits with an error that a long memory adds up token after token, its small part
+//     does not; or the head's fixed number.
 // The state is held column by column ([vdim][dim] per (request, head)): the lanes that own a
 // column read and write its `dim` entries as one contiguous run.
 //
@@ -139,7 +141,7 @@ la_scan_kernel(const float* __restrict__ proj, LaParams p, float* __restrict__ s
     __syncthreads();                              // the tokens staged before are consumed and flushed
     for (int idx = threadIdx.x; idx < STAGE * DP; idx += LA_THREADS) {
       const int j = idx / DP, d = idx - j * DP;
-      float kk = 0.0f, qq = 0.0f, aa = 1.0f;
+      float kk = 0.0f, qq = 0.0f, aa = 0.0f;       // (aa: the decay minus one)
       if (j < n && d < dim) {
         const int token = start + base + j;
         const float* row = proj + (size_t)token * p.ld + (size_t)head * dim;
@@ -148,7 +150,7 @@ la_scan_kernel(const float* __restrict__ proj, LaParams p, float* __restrict__ s
         if (MODE != LA_LOCAL) qq = la_rotated(row + p.q_off, d, p.rot_dims, p.freq, pos) * p.q_scale;
         if (GATED) {
           const float z = p.a_pre[(size_t)token * p.a_ld + (size_t)head * dim + d] + (p.a_bias ? p.a_bias[head * dim + d] : 0.0f);
-          aa = expf(la_log_sigmoid(z) * p.inv_tau);
+          aa = expm1f(la_log_sigmoid(z) * p.inv_tau);
         }
       }
       k_s[j][d] = kk;
@@ -167,14 +169,23 @@ la_scan_kernel(const float* __restrict__ proj, LaParams p, float* __restrict__ s
       for (int r4 = 0; r4 < R4; ++r4) {
         const int d = 4 * (lane + L * r4);
         const float4 kk = *reinterpret_cast<const float4*>(&k_s[j][d]);
-        float4 aa = make_float4(lam, lam, lam, lam);
-        if (GATED) aa = *reinterpret_cast<const float4*>(&a_s[j][d]);
-        S[4 * r4] = fmaf(kk.x, vj, aa.x * S[4 * r4]);
-        S[4 * r4 + 1] = fmaf(kk.y, vj, aa.y * S[4 * r4 + 1]);
-        S[4 * r4 + 2] = fmaf(kk.z, vj, aa.z * S[4 * r4 + 2]);
-        S[4 * r4 + 3] = fmaf(kk.w, vj, aa.w * S[4 * r4 + 3]);
-        if (MODE == LA_LOCAL && GATED) {
-          P[4 * r4] *= aa.x; P[4 * r4 + 1] *= aa.y; P[4 * r4 + 2] *= aa.z; P[4 * r4 + 3] *= aa.w;
+        if (GATED) {
+          const float4 aa = *reinterpret_cast<const float4*>(&a_s[j][d]);      // decays minus one
+          S[4 * r4] += fmaf(aa.x, S[4 * r4], kk.x * vj);
+          S[4 * r4 + 1] += fmaf(aa.y, S[4 * r4 + 1], kk.y * vj);
+          S[4 * r4 + 2] += fmaf(aa.z, S[4 * r4 + 2], kk.z * vj);
+          S[4 * r4 + 3] += fmaf(aa.w, S[4 * r4 + 3], kk.w * vj);
+          if (MODE == LA_LOCAL) {
+            P[4 * r4] = fmaf(aa.x, P[4 * r4], P[4 * r4]);
+            P[4 * r4 + 1] = fmaf(aa.y, P[4 * r4 + 1], P[4 * r4 + 1]);
+            P[4 * r4 + 2] = fmaf(aa.z, P[4 * r4 + 2], P[4 * r4 + 2]);
+            P[4 * r4 + 3] = fmaf(aa.w, P[4 * r4 + 3], P[4 * r4 + 3]);
+          }
+        } else {
+          S[4 * r4] = fmaf(kk.x, vj, lam * S[4 * r4]);
+          S[4 * r4 + 1] = fmaf(kk.y, vj, lam * S[4 * r4 + 1]);
+          S[4 * r4 + 2] = fmaf(kk.z, vj, lam * S[4 * r4 + 2]);
+          S[4 * r4 + 3] = fmaf(kk.w, vj, lam * S[4 * r4 + 3]);
         }
         if (MODE != LA_LOCAL) {
           const float4 qq = *reinterpret_cast<const float4*>(&q_s[j][d]);

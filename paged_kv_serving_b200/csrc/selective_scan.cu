@@ -5,8 +5,9 @@
 //   y[t, c] = sum_n S[c, n] * C[t, n] + D[c] * x[t, c];      out[t, c] = y[t, c] * silu(z[t, c])
 // S lives in a per-request state [slots, inner, state] (float32), read when a portion begins and
 // written back when it ends, so a sequence may arrive in portions of any size and the result is
-// the same operations in the same order however it was cut. Everything that enters the
-// recurrence is float32: the step sizes, the decays, B and C (they arrive as the float32 result
+// the same operations in the same order however it was cut. With float32 activations the decay
+// is applied as S + expm1(dt A) S (a decay close to 1 keeps its small part to full precision).
+// Everything that enters the recurrence is float32: the step sizes, the decays, B and C (they arrive as the float32 result
 // of their projection), the state. x and z are activations in the compute type.
 //
 // A team of L lanes (a power of two, at most a warp) owns one channel; each lane keeps R state
@@ -148,7 +149,13 @@ selective_scan_kernel(const X* __restrict__ x, const X* __restrict__ z, const fl
       float part = 0.0f;
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        S[r] = fmaf(expf(dtv * A[r]), S[r], dx * b_s[j * PADDED + r * L + lane]);
+        if constexpr (sizeof(X) == 4) {
+          // true float32: a decay close to 1 rounds to 24 bits with an error that a long memory adds up token
+          // after token; exp(a) S = S + expm1(a) S keeps the small part to full precision
+          S[r] += fmaf(expm1f(dtv * A[r]), S[r], dx * b_s[j * PADDED + r * L + lane]);
+        } else {
+          S[r] = fmaf(expf(dtv * A[r]), S[r], dx * b_s[j * PADDED + r * L + lane]);
+        }
         part = fmaf(S[r], c_s[j * PADDED + r * L + lane], part);
       }
       y[j] = part;
