@@ -1,0 +1,651 @@
+"""The Segetar design in the engine against the plain implementation of ``plain_segetar`` (``-m gpu``).
+
+Small configurations with random weights, none of them a model anyone serves. They differ from each other in
+every size and option: head counts with and without grouped keys, key and value sizes, rotated parts that do and
+do not cover a head, windows that do and do not fall on page borders, decays, layer orders, a looped span that
+starts at the first layer or later and runs two or three times or not at all, layers without a feed-forward,
+experts in one, two or three groups. Some tests scale queries and keys so that a single key decides a row, which
+makes a window that is one token off, a lost state or a forgotten far token visible.
+"""
+
+from __future__ import annotations
+
+import copy
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_segetar as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ("float32", "bfloat16")
+
+
+def _attention(heads=4, kv_heads=2, dim=16, vdim=16, size=20, rot=None, scale=None):
+    side = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale if scale is not None else dim ** -0.5}
+    if size is not None:
+        side["mask"] = {"size": size}
+    if rot:
+        side["rot"] = {"dims": rot[0], "base": rot[1]}
+    return side
+
+
+def _parallel(left, heads=3, dim=12, vdim=20, tau=8.0, rank=5, left_scale=0.8, right_scale=1.3):
+    return {"type": "parallel", "mixer": {"left": left, "right": {"heads": heads, "dim": dim, "vdim": vdim, "tau": tau, "rank": rank},
+                                          "left_scale": left_scale, "right_scale": right_scale}}
+
+
+def _parallel_2(left, heads=2, dim=16, vdim=12, decay=(0.9, 0.996), rot=(8, 1000.0)):
+    right = {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay)}
+    if rot:
+        right["rot"] = {"dims": rot[0], "base": rot[1]}
+    return {"type": "parallel_2", "mixer": {"left": left, "right": right}}
+
+
+def _mamba(inner=40, state=6, dt_rank=5, conv=4):
+    return {"type": "mamba1", "mixer": {"inner": inner, "state": state, "dt_rank": dt_rank, "conv": conv}}
+
+
+def _moe(experts=6, top=2, ff=24, count=3, keep=2, scale=1.7):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": scale,
+                                                              "groups": {"count": count, "keep": keep}}}
+
+
+def _layer(mixer, mlp):
+    return {**mixer, "mlp": {"kind": "dense", "ff": mlp} if isinstance(mlp, int) else mlp}
+
+
+def _model(layers, vocab=150, width=64, eps=1e-5, loop=None):
+    config = {"architecture": "Segetar", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+    if loop:
+        config["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return config
+
+
+#: "A": every kind of layer; a window of 20 on pages of 8; grouped keys; a rotation of part of a head; two layers
+#: behind the first run three times.
+CONFIG_A = _model([_layer(_mamba(), 72),
+                   _layer(_parallel(_attention(4, 2, 16, 24, size=20, rot=(8, 10000.0))), _moe()),
+                   _layer(_parallel_2(_attention(2, 1, 24, 16, size=13)), _moe(8, 3, 16, 2, 1, 0.9)),
+                   _layer(_mamba(24, 3, 2, 2), None)], loop=(1, 3, 3))
+#: "B": heads of 64 (what the tcgen05 and TMA kernels take) with windows that straddle pages of 16, every query
+#: head with keys of its own in one layer and one key head for all in the other, the whole model looped twice from
+#: its first layer, experts in one group.
+CONFIG_B = _model([_layer(_parallel(_attention(2, 1, 64, 64, size=40, rot=(64, 500000.0)), 2, 32, 16, 16.0, 8, 1.2, 0.5), _moe(4, 2, 32, 1, 1, 1.5)),
+                   _layer(_parallel_2(_attention(2, 2, 64, 64, size=21), 1, 32, 32, (0.97,), (32, 50.0)), 48),
+                   _layer(_mamba(64, 16, 8, 3), _moe(4, 1, 16, 2, 2, 1.0))],
+                  vocab=97, width=128, eps=1e-6, loop=(0, 3, 2))
+#: "C": sizes that are no multiples of 8, some of them odd; no loop; a window longer than the prompts and one of a
+#: single token; a convolution of one tap; no rotation anywhere; a decay of exactly 1.
+CONFIG_C = _model([_layer(_parallel_2(_attention(3, 1, 10, 7, size=300), 3, 6, 5, (0.5, 0.9, 1.0), None), None),
+                   _layer(_mamba(18, 5, 3, 1), 22),
+                   _layer(_parallel(_attention(2, 2, 14, 6, size=1), 1, 9, 7, 2.0, 3, 1.0, 1.0), _moe(5, 5, 9, 1, 1, 2.5)),
+                   _layer(_parallel(_attention(6, 3, 6, 10, size=5, rot=(2, 37.0)), 2, 10, 4, 30.0, 1, 0.3, 2.0), 18)],
+                  vocab=77, width=52, eps=1e-4)
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C}
+PAGE = {"A": 8, "B": 16, "C": 4}
+
+
+def _specs(config):
+    from paged_kv_serving_b200.config import registry
+    from paged_kv_serving_b200.config.segetar_config import SegetarConfig
+
+    typed = SegetarConfig.from_dict(config)
+    return typed, registry.architecture("Segetar").layout(typed).tensor_specs()
+
+
+def random_tensors(config, seed, scale=1.0):
+    """Random tensors, rounded to bfloat16 so that both number formats hold the same values."""
+    _, specs = _specs(config)
+    rng = np.random.default_rng(seed)
+    out = {}
+    for name in sorted(specs):
+        shape = specs[name].shape
+        last = name.rsplit(".", 1)[-1]
+        if last == "A_log":
+            values = rng.uniform(-3.0, 1.0, size=shape)
+        elif name.endswith("dt.b"):
+            values = rng.uniform(-4.0, -1.0, size=shape)
+        elif name.endswith("a2.b"):
+            values = rng.uniform(1.0, 5.0, size=shape)
+        elif last == "D" or last in ("norm1", "norm2", "norm", "out") or name.endswith((".q.norm", ".k.norm")):
+            values = 1.0 + 0.3 * rng.standard_normal(shape)
+        elif last == "correction":
+            values = 0.3 * rng.standard_normal(shape)
+        elif last == "conv":
+            values = 0.5 * rng.standard_normal(shape)
+        elif name.endswith(".b") or name == "loop.step":
+            values = 0.3 * rng.standard_normal(shape)
+        elif name == "embed":
+            values = rng.standard_normal(shape)
+        else:
+            values = scale * rng.standard_normal(shape) / math.sqrt(shape[-1])
+        out[name] = torch.from_numpy(np.asarray(values, dtype=np.float32)).to(torch.bfloat16)
+    return out
+
+
+def build(config, tensors, dtype):
+    from paged_kv_serving_b200.models.decoder import DecoderModel
+
+    typed, _ = _specs(config)
+    return DecoderModel.from_tensors(typed, tensors, dtype=dtype, device="cuda")
+
+
+def session_for(config, tensors, dtype, max_tokens=512, page=8, max_live=4):
+    from paged_kv_serving_b200.engine.replay import ReplaySession
+
+    session = ReplaySession(build(config, tensors, dtype), max_tokens=max_tokens, block_size=page, max_live=max_live)
+    session.runner.storage.fill(float("nan"))        # a page that was never written must never be read
+    return session
+
+
+def tokens_for(config, count, seed):
+    return [int(t) for t in np.random.default_rng(seed).integers(0, config["vocab"], size=count)]
+
+
+def row_errors(got, want):
+    got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape, f"shapes {got.shape} and {want.shape}"
+    assert np.isfinite(got).all(), "the engine's logits are not finite"
+    gap = got - want
+    gap = gap - gap.mean(axis=-1, keepdims=True)
+    return np.sqrt((gap ** 2).mean(axis=-1)) / max(float(want.std()), 1e-6)
+
+
+def close(got, want, dtype, what, bf16_bound=0.12, bf16_typical=0.05):
+    """Rows of logits against the plain ones: the gap with its mean taken off, as a share of the spread of the plain
+    logits. float32: every row within 2e-4. bfloat16: rounding moves a row by about a percent; where two experts'
+    choice scores nearly tie it may pick the other expert, which moves that token's row by tens of percent and, through
+    cache and state, later rows by a few. So the typical row stays within ``bf16_typical``, at most one row in six may
+    exceed ``bf16_bound``, none 150 %. The float32 runs of the same schedules are the sharp test."""
+    error = row_errors(got, want)
+    worst = f"{what}: row {int(error.argmax())} is off by {error.max():.3e} of the spread"
+    if dtype == "float32":
+        assert float(error.max()) <= 2e-4, worst
+    else:
+        assert float(np.median(error)) <= bf16_typical, f"{what}: the typical row is off by {np.median(error):.3e} of the spread"
+        assert int((error > bf16_bound).sum()) <= max(1, error.size // 6), worst
+        assert float(error.max()) <= 1.5, worst
+
+
+def plain_logits(config, tensors, tokens):
+    return plain.forward(tensors, config, tokens).numpy()
+
+
+# --- whole models: prompts, decoding, portions, batches --------------------------------------------
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_whole_prompt_every_position_first_tokens_included(name, dtype):
+    config = CONFIGS[name]
+    tensors = random_tensors(config, seed=3)
+    tokens = tokens_for(config, 70, seed=1)
+    session = session_for(config, tensors, dtype, page=PAGE[name])
+    got = session.step([{"id": "r", "tokens": tokens, "want": list(range(len(tokens)))}], end=["r"])
+    close(got, plain_logits(config, tensors, tokens), dtype, f"{name} whole prompt")
+    session.check_invariants()
+
+
+@pytest.mark.parametrize("name", ("A", "B"))
+def test_the_residual_stream_after_every_layer_run_in_float32(name):
+    config = CONFIGS[name]
+    tensors = random_tensors(config, seed=12)
+    tokens = tokens_for(config, 33, seed=5)
+    _, want = plain.forward(tensors, config, tokens, return_layers=True)
+    session = session_for(config, tensors, "float32", page=PAGE[name])
+    seen = []
+    for block in session.model.layout.blocks:
+        inner = block.forward
+
+        def spy(hidden, pending, ctx, binding, next_norm=None, _inner=inner):
+            out = _inner(hidden, pending, ctx, binding, next_norm=next_norm)
+            seen.append(hidden.clone() if not isinstance(out, torch.Tensor) else hidden + out.float())
+            return out
+
+        block.forward = spy
+    session.step([{"id": "r", "tokens": tokens, "want": [len(tokens) - 1]}])
+    assert len(seen) == len(plain.run_order(config)) == {"A": 8, "B": 6}[name]
+    for index, stream in enumerate(seen):
+        gap = np.abs(stream.cpu().numpy() - want[index].numpy()).max()
+        assert gap <= 1e-4 * float(want[index].abs().max()), f"the stream after layer run {index} is off by {gap:.3e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_prompt_then_token_by_token_across_windows_and_pages(name, dtype):
+    config = CONFIGS[name]
+    tensors = random_tensors(config, seed=4)
+    tokens = tokens_for(config, 75, seed=2)
+    want = plain_logits(config, tensors, tokens)
+    session = session_for(config, tensors, dtype, page=PAGE[name])
+    bulk = 21
+    rows = [session.step([{"id": "r", "tokens": tokens[:bulk], "want": [bulk - 1]}])]
+    for t in tokens[bulk:]:
+        rows.append(session.step([{"id": "r", "tokens": [t], "want": [0]}]))
+    close(np.concatenate(rows), want[bulk - 1:], dtype, f"{name} prompt then decoding")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decoding_from_the_very_first_token_and_for_long(dtype):
+    """Every token alone from position 0 (zero states, an empty convolution tail) for 170 steps: decode steps replay a
+    captured graph, pages behind the windows go back to the pool."""
+    config = CONFIGS["A"]
+    tensors = random_tensors(config, seed=5)
+    tokens = tokens_for(config, 170, seed=3)
+    want = plain_logits(config, tensors, tokens)
+    session = session_for(config, tensors, dtype, max_tokens=192, page=4)
+    rows = [session.step([{"id": "r", "tokens": [t], "want": [0]}]) for t in tokens]
+    close(np.concatenate(rows), want, dtype, "decoding from the first token")
+    given_back = max(sum(1 for page in table if page == -1) for table in session.live["r"].block_tables)
+    assert given_back >= 30, "pages behind the window were not given back"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_portions_of_changing_size_down_to_two_tokens(name, dtype):
+    config = CONFIGS[name]
+    tensors = random_tensors(config, seed=6)
+    tokens = tokens_for(config, 90, seed=4)
+    want = plain_logits(config, tensors, tokens)
+    session = session_for(config, tensors, dtype, page=PAGE[name])
+    rows, at = [], 0
+    for size in [2, 3, 1, 2, 17, 2, 1, 1, 31, 5, 2, 9, 2, 2, 10]:
+        part = tokens[at:at + size]
+        rows.append(session.step([{"id": "r", "tokens": part, "want": list(range(len(part)))}]))
+        at += len(part)
+    assert at == len(tokens)
+    close(np.concatenate(rows), want, dtype, f"{name} portions")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_long_prompt_in_chunks_of_the_scan_and_in_long_portions(dtype):
+    """300 tokens at once (the linear attention cuts them into chunks that run side by side), and the same in portions
+    of 150 + 2 + 148."""
+    config = CONFIGS["B"]
+    tensors = random_tensors(config, seed=15)
+    tokens = tokens_for(config, 300, seed=6)
+    want = plain_logits(config, tensors, tokens)
+    session = session_for(config, tensors, dtype, page=16)
+    places = list(range(0, 300, 7)) + [299]
+    got = session.step([{"id": "r", "tokens": tokens, "want": places}], end=["r"])
+    close(got, want[places], dtype, "a long prompt")
+    rows = [session.step([{"id": "s", "tokens": tokens[a:b], "want": [b - a - 2, b - a - 1]}]) for a, b in ((0, 150), (150, 152), (152, 300))]
+    close(np.concatenate(rows), want[[148, 149, 150, 151, 298, 299]], dtype, "a long prompt in portions")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ("A", "B"))
+def test_unequal_requests_in_one_batch_equal_each_alone_and_slots_and_pages_are_used_again(name, dtype):
+    """Three requests of different lengths advance side by side in portions and single tokens, in a pool of two state
+    slots and few pages: a fourth and a fifth request start in the slot and on the pages a finished one gave back."""
+    config = CONFIGS[name]
+    tensors = random_tensors(config, seed=7)
+    lengths = {"a": 50, "b": 23, "c": 9, "d": 41, "e": 30}
+    tokens = {k: tokens_for(config, n, seed=10 + i) for i, (k, n) in enumerate(lengths.items())}
+    want = {k: plain_logits(config, tensors, v) for k, v in tokens.items()}
+    session = session_for(config, tensors, dtype, max_tokens=128, page=PAGE[name], max_live=2)
+    got = {k: [] for k in tokens}
+    at = {k: 0 for k in tokens}
+
+    def step(plan):
+        entries, order, end = [], [], []
+        for key, count in plan:
+            part = tokens[key][at[key]:at[key] + count]
+            entries.append({"id": key, "tokens": part, "want": list(range(len(part)))})
+            order.append((key, len(part)))
+            at[key] += len(part)
+            if at[key] == len(tokens[key]):
+                end.append(key)
+        out = session.step(entries, end=end)
+        row = 0
+        for key, n in order:
+            got[key].append(out[row:row + n])
+            row += n
+        session.check_invariants()
+
+    step([("a", 13), ("b", 2)])
+    step([("a", 1), ("b", 19)])
+    step([("a", 30), ("b", 1)])
+    step([("a", 1), ("b", 1)])            # b ends: its slot and pages go back
+    step([("a", 1), ("c", 7)])            # c takes them
+    step([("a", 1), ("c", 1)])
+    step([("c", 1), ("a", 3)])            # both end
+    step([("d", 2), ("e", 30)])           # e is whole in one step and ends
+    step([("d", 39)])
+    if dtype == "float32":
+        for key in tokens:
+            close(np.concatenate(got[key]), want[key], dtype, f"{name} request {key} in a batch")
+    else:
+        # (a swapped expert early in a short request moves most of its few rows: the rule for bfloat16 rows is
+        # applied to the rows of all requests together)
+        close(np.concatenate([row for key in tokens for row in got[key]]), np.concatenate([want[key] for key in tokens]), dtype,
+              f"{name} requests in a batch")
+    assert session.cache.num_free_blocks == session.num_blocks and session.cache.state_slots.num_free == 2
+
+
+def test_logits_do_not_depend_on_the_cut_in_float32():
+    config = CONFIGS["A"]
+    tensors = random_tensors(config, seed=8)
+    tokens = tokens_for(config, 60, seed=9)
+    whole = session_for(config, tensors, "float32").step([{"id": "r", "tokens": tokens, "want": list(range(60))}])
+    session = session_for(config, tensors, "float32")
+    parts = [session.step([{"id": "r", "tokens": tokens[i:i + 1], "want": [0]}]) for i in range(60)]
+    assert np.abs(np.concatenate(parts) - whole).max() <= 2e-5 * np.abs(whole).max()
+    session = session_for(config, tensors, "float32")
+    parts = [session.step([{"id": "r", "tokens": tokens[i:i + 7], "want": list(range(len(tokens[i:i + 7])))}])
+             for i in range(0, 60, 7)]
+    assert np.abs(np.concatenate(parts) - whole).max() <= 2e-5 * np.abs(whole).max()
+
+
+# --- faults that random weights would hide ------------------------------------------------------------
+
+
+def _sharpen(tensors, prefix, factor):
+    """Scale an attention's query and key norm weights so that its softmax picks the one best key of a row."""
+    out = dict(tensors)
+    for name in (prefix + "q.norm", prefix + "k.norm"):
+        out[name] = (tensors[name].float() * factor).to(torch.bfloat16)
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,layer", (("A", 1), ("A", 2), ("B", 0), ("B", 1), ("C", 3)))
+def test_sharp_attention_shows_a_window_that_is_one_token_off(name, layer, dtype):
+    """With queries and keys scaled up the softmax of the layer's attention side is nearly a choice of one key; a key
+    just outside the window that is let in, or one just inside that is left out, then moves whole rows."""
+    config = CONFIGS[name]
+    # (scores nine times as large in float32; four times in bfloat16, whose rounding of keys a sharper softmax
+    # would turn into other choices)
+    tensors = _sharpen(random_tensors(config, seed=21), f"l{layer}.mix.left.", 3.0 if dtype == "float32" else 2.0)
+    tokens = tokens_for(config, 80, seed=22)
+    want = plain_logits(config, tensors, tokens)
+    # the sharpened model is a different model: the window's edge must matter in the plain implementation itself
+    wider = copy.deepcopy(config)
+    wider["layers"][layer]["mixer"]["left"]["mask"]["size"] += 1
+    assert row_errors(plain_logits(wider, tensors, tokens), want).max() > 0.01, "the test's weights do not show the window's edge"
+    session = session_for(config, tensors, dtype, page=PAGE[name])
+    got = [session.step([{"id": "r", "tokens": tokens[:47], "want": list(range(47))}])]
+    got += [session.step([{"id": "r", "tokens": [t], "want": [0]}]) for t in tokens[47:]]
+    # (a softmax that is nearly a choice also magnifies what bfloat16 rounds away: the float32 run is the sharp one)
+    close(np.concatenate(got), want, dtype, f"{name} layer {layer} with a sharp softmax", bf16_bound=0.5, bf16_typical=0.2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_far_token_reaches_through_the_states_only(dtype):
+    """Two prompts that differ in their first token alone: 200 tokens on, far outside every window, the logits still
+    differ (through the recurrent states and the looped passes), in the engine as in the plain implementation."""
+    config = CONFIGS["B"]
+    tensors = random_tensors(config, seed=23, scale=1.3)
+    # slow decays, so that the first token is still felt
+    for name in list(tensors):
+        if name.endswith("A_log"):
+            tensors[name] = torch.full_like(tensors[name], -4.0)
+        if name.endswith("a2.b"):
+            tensors[name] = torch.full_like(tensors[name], 8.0)
+    tokens = tokens_for(config, 200, seed=24)
+    other = [(tokens[0] + 1) % config["vocab"]] + tokens[1:]
+    want, want_other = plain_logits(config, tensors, tokens)[-3:], plain_logits(config, tensors, other)[-3:]
+    felt = row_errors(want_other, want).min()
+    assert felt > 5e-3, "the test's weights do not carry the first token this far"
+    for ids, expected, not_expected in ((tokens, want, want_other), (other, want_other, want)):
+        session = session_for(config, tensors, dtype, page=16)
+        session.step([{"id": "r", "tokens": ids[:130], "want": []}])
+        session.step([{"id": "r", "tokens": ids[130:197], "want": []}])
+        got = [session.step([{"id": "r", "tokens": [t], "want": [0]}]) for t in ids[197:]]
+        error = row_errors(np.concatenate(got), expected)
+        if dtype == "float32":
+            assert error.max() <= 2e-4, f"off by {error.max():.3e}, the first token moves rows by {felt:.3e}"
+        else:
+            # every row is nearer to its own prompt's plain row than to the other prompt's
+            assert (error < row_errors(np.concatenate(got), not_expected)).all() and error.max() < felt
+
+
+# --- mechanisms alone -----------------------------------------------------------------------------------
+
+
+def test_router_chooses_within_the_best_groups_and_weighs_by_the_uncorrected_scores():
+    from paged_kv_serving_b200.ops import mixer_ops
+
+    rng = torch.Generator().manual_seed(31)
+    for experts, top, count, keep, scale in ((12, 3, 4, 2, 1.5), (8, 2, 8, 3, 1.0), (6, 6, 1, 1, 0.5), (16, 4, 2, 1, 2.5), (9, 2, 3, 1, 1.0)):
+        logits = torch.randn((50, experts), generator=rng, dtype=torch.float64) * 2.0
+        correction = torch.randn((experts,), generator=rng, dtype=torch.float64)          # large: it changes choices
+        router = {"experts": experts, "top": top, "scale": scale, "groups": {"count": count, "keep": keep}}
+        # (with the identity as the router's matrix the rows of ``logits`` are the logits)
+        want = plain.router_weights(logits, {"router": torch.eye(experts, dtype=torch.float64), "correction": correction}, router)
+        padded = torch.zeros((50, experts + 3), dtype=torch.float32)
+        padded[:, :experts] = logits.float()
+        got = mixer_ops.route_scored(padded.cuda(), experts, top, correction.float().cuda(), count, keep, scale).cpu().double()
+        assert ((got != 0) == (want != 0)).all(), "another choice of experts"
+        assert (got != 0).sum(dim=1).eq(top).all()
+        assert (got - want).abs().max() < 1e-5
+        # the correction decides choices but is not part of a weight
+        uncorrected = plain.router_weights(logits, {"router": torch.eye(experts, dtype=torch.float64), "correction": correction * 0}, router)
+        if top < experts // count * keep:
+            assert ((uncorrected != 0) != (want != 0)).any()
+
+
+@pytest.mark.parametrize("gated", (True, False))
+def test_linear_attention_kernel_in_a_row_and_in_chunks_over_ragged_entries(gated):
+    """The scan alone: entries of 1 to 300 tokens that start from given states, once with every entry walked in a row
+    and once cut into chunks; both against the plain recurrence, states included."""
+    from paged_kv_serving_b200.ops import mixer_ops
+
+    rng = torch.Generator().manual_seed(41)
+    heads, dim, vdim = 3, 20, 12
+    lens = [1, 300, 2, 77, 130]
+    tokens = sum(lens)
+    offsets = {"q": 0, "k": 64, "v": 128, "g": 168}
+    proj = torch.randn((tokens, 208), generator=rng, dtype=torch.float64) * 0.5
+    pre = torch.randn((tokens, heads * dim), generator=rng, dtype=torch.float64) + 3.0
+    bias = torch.randn((heads * dim,), generator=rng, dtype=torch.float64)
+    weight = 1.0 + 0.2 * torch.randn((vdim,), generator=rng, dtype=torch.float64)
+    fixed = torch.tensor([0.5, 0.97, 1.0], dtype=torch.float64)
+    state0 = torch.randn((len(lens) + 2, heads, vdim, dim), generator=rng, dtype=torch.float64)
+    slots = [4, 0, 6, 2, 1]
+    starts = np.concatenate([[0], np.cumsum(lens)])
+    positions = torch.cat([torch.arange(n) + 5 * i for i, n in enumerate(lens)])
+    freq = torch.tensor([10.0 ** (-2.0 * i / 8) for i in range(4)], dtype=torch.float64)
+
+    def plain_entry(a, b, slot):
+        q = proj[a:b, 0:heads * dim].view(-1, heads, dim)
+        k = proj[a:b, 64:64 + heads * dim].view(-1, heads, dim)
+        v = proj[a:b, 128:128 + heads * vdim].view(-1, heads, vdim)
+        g = proj[a:b, 168:168 + heads * vdim]
+        if gated:
+            decay = (torch.sigmoid(pre[a:b] + bias) ** (1.0 / 7.0)).view(-1, heads, dim)
+            q = q * 0.3
+        else:
+            decay = fixed[None, :, None].expand(b - a, heads, dim)
+            q = plain.rotate_halves(q, positions[a:b], 8, 10.0)
+            k = plain.rotate_halves(k, positions[a:b], 8, 10.0) * 0.4
+        S = state0[slot].transpose(1, 2).clone()                     # [heads, dim, vdim]
+        out = torch.zeros((b - a, heads, vdim), dtype=torch.float64)
+        for t in range(b - a):
+            S = decay[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
+            out[t] = torch.einsum("hdv,hd->hv", S, q[t])
+        out = plain.unit_rms(out, 1e-5) * (weight if gated else 1.0)
+        return out.reshape(b - a, -1) * plain.silu(g) * 1.5, S.transpose(1, 2)
+
+    want = [plain_entry(int(starts[i]), int(starts[i + 1]), slots[i]) for i in range(len(lens))]
+    for in_a_row in (1 << 30, 128):
+        mixer_ops.LINEAR_ATTENTION_IN_A_ROW, before = in_a_row, mixer_ops.LINEAR_ATTENTION_IN_A_ROW
+        try:
+            state = state0.float().cuda()
+            kwargs = dict(decay_pre=pre.float().cuda(), decay_bias=bias.float().cuda(), inv_tau=1.0 / 7.0, q_scale=0.3,
+                          norm_weight=weight.float().cuda()) if gated else \
+                dict(head_decay=fixed.float().cuda(), k_scale=0.4, rot_dims=8, freq=freq.float().cuda(),
+                     positions=positions.int().cuda())
+            wide = torch.zeros((tokens, heads * vdim + 8), dtype=torch.float32, device="cuda")
+            got = mixer_ops.linear_attention(proj.float().cuda(), offsets, state, torch.tensor(starts, dtype=torch.int32).cuda(),
+                                             torch.tensor(slots, dtype=torch.int32).cuda(), heads, dim, vdim, torch.float32,
+                                             eps=1e-5, out_factor=1.5, out=wide[:, 4:4 + heads * vdim], **kwargs)
+            torch.cuda.synchronize()
+        finally:
+            mixer_ops.LINEAR_ATTENTION_IN_A_ROW = before
+        assert (wide[:, :4] == 0).all() and (wide[:, 4 + heads * vdim:] == 0).all(), "written beside its columns"
+        for i, (rows, last) in enumerate(want):
+            a, b = int(starts[i]), int(starts[i + 1])
+            assert (got[a:b].cpu().double() - rows).abs().max() <= 2e-4 * rows.abs().max(), f"entry {i}"
+            assert (state[slots[i]].cpu().double() - last).abs().max() <= 2e-5 * last.abs().max(), f"state of entry {i}"
+        untouched = [s for s in range(state0.shape[0]) if s not in slots]
+        assert torch.equal(state[untouched].cpu(), state0[untouched].float())
+
+
+def test_query_and_key_preparation_with_biases_joint_norm_and_neighbour_pairs():
+    """The kernel in front of the attention alone, through a part with every option of the design's fuller side: the
+    scores of its prepared queries and cached keys equal those of the plain biases, norm over the whole projection
+    and rotation of neighbouring pairs (the part reorders rows, which no score shows); values are cached with their
+    bias."""
+    from paged_kv_serving_b200 import ops
+    from paged_kv_serving_b200.ops import mixer_ops
+    from paged_kv_serving_b200.parts import ScaledRotaryFrequencies, SinkWindowAttention
+
+    H, G, dim, vdim, width, page, n = 4, 2, 16, 24, 48, 4, 23
+    part = SinkWindowAttention(width, H, G, dim, vdim, 0.21, rotary=ScaledRotaryFrequencies(12, 300.0), unit_norm=True, eps=1e-5,
+                               window=11, norm_weights=True, joint_norm=True, bias=True, pairing="interleaved", head_gate=True)
+    rng = np.random.default_rng(51)
+    params = {name: torch.from_numpy(rng.standard_normal(spec.shape).astype(np.float32)) for name, spec in part.param_specs().items()}
+    part.load({name: t.cuda() for name, t in params.items()})
+    h = torch.from_numpy(rng.standard_normal((n, width)).astype(np.float32))
+    positions = torch.arange(n) * 3 + 2
+    qkv = (h.cuda() @ part.qkv.T).contiguous()
+    k_pool = torch.zeros((8, G, page, dim), dtype=torch.float32, device="cuda")
+    v_pool = torch.zeros((8, G, page, vdim), dtype=torch.float32, device="cuda")
+    slots = torch.randperm(8 * page, generator=torch.Generator().manual_seed(1))[:n].int()
+    mixer_ops.qkv_prepare(qkv, positions.int().cuda(), part.rotary.device_frequencies(torch.device("cuda")), 12, 1.0, 1e-5, True, k_pool,
+                          v_pool, slots.cuda(), H, G, dim, vdim, page, ops.status_word(torch.device("cuda")), q_weight=part.q_norm,
+                          k_weight=part.k_norm, bias=part.qkv_bias, joint_norm=True)
+    q_got = qkv[:, :H * dim].view(n, H, dim).cpu().double()
+    at = slots.long()
+    k_got = k_pool.cpu().double()[at // page, :, at % page]            # [n, G, dim]
+    v_got = v_pool.cpu().double()[at // page, :, at % page]
+    p = {name: t.double() for name, t in params.items()}
+    x = h.double()
+    q = plain.rotate_neighbours((plain.unit_rms(x @ p["q"].T + p["q_b"], 1e-5) * p["q_norm"]).view(n, H, dim), positions, 12, 300.0)
+    k = plain.rotate_neighbours((plain.unit_rms(x @ p["k"].T + p["k_b"], 1e-5) * p["k_norm"]).view(n, G, dim), positions, 12, 300.0)
+    want = torch.einsum("ihd,jgd->hgij", q, k)
+    got = torch.einsum("ihd,jgd->hgij", q_got, k_got)
+    assert (got - want).abs().max() <= 1e-4 * want.abs().max()
+    assert (v_got - (x @ p["v"].T + p["v_b"]).view(n, G, vdim)).abs().max() <= 1e-5
+    # the gate's columns lie behind the values' and are left as the product made them
+    assert torch.equal(qkv[:, part.gate_at:part.gate_at + H].cpu(), (h.cuda() @ part.qkv.T)[:, part.gate_at:part.gate_at + H].cpu())
+
+
+# --- greedy generation through the entry point and the scheduler ------------------------------------
+
+
+def _plain_choice(config, tensors, prompt, ids, slack):
+    rows = plain_logits(config, tensors, list(prompt) + ids[:-1])[len(prompt) - 1:]
+    return all(row[token] >= row.max() - slack(row) for token, row in zip(ids, rows))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_the_entry_point(tmp_path, dtype):
+    from paged_kv_serving_b200.api import generate
+    from paged_kv_serving_b200.weights.random_init import write_model_folder
+
+    config = CONFIGS["A"]
+    typed, _ = _specs(config)
+    tensors = random_tensors(config, seed=11, scale=1.5)
+    write_model_folder(tmp_path, typed, tensors)
+    prompts = [tokens_for(config, n, seed=20 + n) for n in (5, 33, 18)]
+    got = generate(tmp_path, prompts, max_new_tokens=12, dtype=dtype, block_size=8, max_batched_tokens=24, max_running_seqs=4)
+    for prompt, samples in zip(prompts, got):
+        ids = samples[0]
+        assert len(ids) == 12
+        assert _plain_choice(config, tensors, prompt, ids, (lambda row: 1e-4) if dtype == "float32" else (lambda row: 0.1 * row.std()))
+
+
+def test_forked_samples_share_pages_and_copy_states(tmp_path):
+    from paged_kv_serving_b200.api import generate
+    from paged_kv_serving_b200.weights.random_init import write_model_folder
+
+    config = CONFIGS["A"]
+    typed, _ = _specs(config)
+    tensors = random_tensors(config, seed=13, scale=1.5)
+    write_model_folder(tmp_path, typed, tensors)
+    prompt = tokens_for(config, 29, seed=14)
+    got = generate(tmp_path, [prompt], max_new_tokens=9, n=3, dtype="float32", block_size=8, max_batched_tokens=64, max_running_seqs=4)
+    assert len(got[0]) == 3 and all(ids == got[0][0] for ids in got[0]), "greedy samples of one prompt differ"
+    assert _plain_choice(config, tensors, prompt, got[0][0], lambda row: 1e-4)
+
+
+def test_a_cramped_pool_preempts_and_recomputes_states_and_pages():
+    """Four requests in a pool that holds two: requests are preempted, give back pages and state slot, and start again
+    from position 0 in a cleared slot; every request's tokens are still the plain greedy continuation."""
+    from paged_kv_serving_b200.api import engine_for
+    from paged_kv_serving_b200.engine.sequence import Request, SamplingParams
+
+    config = copy.deepcopy(CONFIGS["A"])
+    for layer in config["layers"]:
+        if layer["type"] != "mamba1":
+            layer["mixer"]["left"]["mask"] = {"size": 500}       # nothing leaves the window: pages pile up
+    tensors = random_tensors(config, seed=15, scale=1.5)
+    prompts = [tokens_for(config, n, seed=30 + n) for n in (41, 37, 44, 29)]
+    new = 22
+    engine = engine_for(build(config, tensors, "float32"), prompts, max_new_tokens=new, dtype="float32", block_size=8, num_blocks=20,
+                        max_batched_tokens=48, max_running_seqs=4)
+    for i, prompt in enumerate(prompts):
+        assert engine.submit(Request(request_id=f"r{i}", prompt_token_ids=tuple(prompt), sampling=SamplingParams(max_new_tokens=new))).admitted
+    outputs = {o.request_id: o for o in engine.run_until_idle()}
+    assert engine.scheduler.stats.preemptions > 0, "the cramped pool must preempt"
+    for i, prompt in enumerate(prompts):
+        ids = list(outputs[f"r{i}"].samples[0].token_ids)
+        rows = plain_logits(config, tensors, list(prompt) + ids[:-1])[len(prompt) - 1:]
+        assert len(ids) == new and all(row[token] >= row.max() - 1e-4 for token, row in zip(ids, rows)), f"request {i}"
+
+
+def test_command_line_checkpoint_generation_and_trace_program(tmp_path):
+    """The design through the command line as a user meets it: a random-weights folder from a ``config.json``, greedy
+    generation from it, and ``bin/trace_run`` replaying a trace of it with two live requests."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from safetensors.torch import load_file
+
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, PYTHONPATH=str(root))
+    config = CONFIGS["C"]
+    model_dir, out_dir = tmp_path / "model", tmp_path / "out"
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    made = subprocess.run([sys.executable, "-m", "paged_kv_serving_b200", "build-checkpoint", "--out", str(model_dir),
+                           "--config", str(tmp_path / "config.json"), "--seed", "3", "--dtype", "bfloat16", "--std", "0.15"],
+                          capture_output=True, text=True, env=env, check=True)
+    tensors = load_file(str(model_dir / "model.safetensors"))
+    assert json.loads(made.stdout)["parameters"] == sum(t.numel() for t in tensors.values())
+    assert float(tensors["l2.mix.right.a2.b"].float().mean()) > 1.0 and float(tensors["l1.mix.A_log"].float().std()) > 0.1, \
+        "the random-weights mode draws slow decays and decay logarithms with a spread"
+    run = subprocess.run([sys.executable, "-m", "paged_kv_serving_b200", "generate", "--model", str(model_dir),
+                          "--prompt-ids", "5,17,3,20", "--max-new-tokens", "6", "--dtype", "float32", "--block-size", "4"],
+                         capture_output=True, text=True, env=env, check=True)
+    line = [json.loads(text) for text in run.stdout.splitlines() if text.startswith("{")][0]
+    ids = line["samples"][0]
+    rows = plain_logits(config, tensors, [5, 17, 3, 20] + ids[:-1])[3:]
+    assert len(ids) == 6 and all(row[token] >= row.max() - 1e-4 for token, row in zip(ids, rows))
+
+    a, b = tokens_for(config, 30, seed=9), tokens_for(config, 12, seed=10)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:21], "want": [0, 20]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[21:23], "want": []}, {"id": "b", "tokens": b[:11], "want": [3]}], "end": []},
+             {"step": 2, "entries": [{"id": "b", "tokens": b[11:], "want": [0]}, {"id": "a", "tokens": a[23:], "want": [6]}], "end": ["a", "b"]}]
+    process = subprocess.Popen([str(root / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", "float32",
+                                "--out", str(out_dir), "--max-tokens", "128", "--block-size", "4"],
+                               stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
+    for record in steps:
+        process.stdin.write(json.dumps(record) + "\n")
+        process.stdin.flush()
+        assert process.stdout.readline().strip() == f"done {record['step']}"
+    process.stdin.close()
+    assert process.wait(timeout=120) == 0
+    want_a, want_b = plain_logits(config, tensors, a), plain_logits(config, tensors, b)
+    read = lambda step: np.fromfile(out_dir / f"{step}.f32", dtype="<f4").reshape(-1, config["vocab"])
+    close(read(0), want_a[[0, 20]], "float32", "trace step 0")
+    close(read(1), want_b[[3]], "float32", "trace step 1")
+    close(read(2), np.stack([want_b[11], want_a[29]]), "float32", "trace step 2")
