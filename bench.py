@@ -494,7 +494,9 @@ def run_design(args) -> dict:
     Revupel beside the Llama-style decoder; Tiburax beside Revupel (the closest model: attention and
     a recurrent mixer in turn, routed experts) and the Llama-style decoder; Rodelix beside Revupel
     (the closest model: attention over a cached latent and a matrix-state recurrence in turn), Tiburax
-    (whose window attention is the like of Rodelix's) and the Llama-style decoder."""
+    (whose window attention is the like of Rodelix's) and the Llama-style decoder; Segetar beside Tiburax (the closest
+    model: window attention, Mamba blocks and gated routed experts), Rodelix (whose linear attention with a matrix state is
+    the like of Segetar's) and the Llama-style decoder."""
     import torch
 
     from paged_kv_serving_b200 import design_bench
@@ -512,11 +514,14 @@ def run_design(args) -> dict:
 
     for size in [s for s in args.design_sizes.split(",") if s]:
         sizes[size] = {}
-        if args.design == "rodelix":
+        if args.design == "segetar":
+            sizes[size]["segetar"] = measured(design_bench.segetar_config(size))
+        if args.design in ("rodelix", "segetar"):
             sizes[size]["rodelix"] = measured(design_bench.rodelix_config(size))
-        if args.design in ("tiburax", "rodelix"):
+        if args.design in ("tiburax", "rodelix", "segetar"):
             sizes[size]["tiburax"] = measured(design_bench.tiburax_config(size))
-        sizes[size]["revupel"] = measured(design_bench.revupel_config(size))
+        if args.design != "segetar":
+            sizes[size]["revupel"] = measured(design_bench.revupel_config(size))
         sizes[size]["llama_style"] = measured(design_bench.llama_like(size))
     clocks.stop()
     return {"impl": "ours", "design": args.design, "dtype": "bf16", "data": "synthetic: random ids, random N(0, 0.02) weights",
@@ -541,7 +546,7 @@ def main() -> int:
     parser.add_argument("--only-workloads", action="store_true", help="leave out the headline run (for profiling a workload)")
     parser.add_argument("--workload-layers", type=int, default=0, help="fewer layers for those workloads (0: all)")
     parser.add_argument("--serve-requests", type=int, default=256)
-    parser.add_argument("--design", choices=("revupel", "tiburax", "rodelix"), default=None,
+    parser.add_argument("--design", choices=("revupel", "tiburax", "rodelix", "segetar"), default=None,
                         help="instead of the default run: prefill and decode throughput of this design at layer sizes of "
                              "real models, beside the framework's closest models at equal sizes, with every kernel against its roofline")
     parser.add_argument("--design-sizes", default="1b,7b", help="which of the sizes of paged_kv_serving_b200.design_bench")

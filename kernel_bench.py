@@ -5,7 +5,7 @@ rotates over 32 layers' worth of buffers (so that weights, keys and values come 
 a real step) and reports microseconds per launch with the achieved bandwidth or arithmetic rate.
 The sizes come from a preset of ``config/presets.py``; nothing here is used by the engine.
 
-    python kernel_bench.py [gemm] [decode-gemm] [prefill-attention] [decode-attention] [elementwise] [scan] [sink-attention] [lightning]
+    python kernel_bench.py [gemm] [decode-gemm] [prefill-attention] [decode-attention] [elementwise] [scan] [sink-attention] [lightning] [linear-attention]
 """
 
 from __future__ import annotations
@@ -250,6 +250,43 @@ def bench_lightning(config, page: int) -> None:
               f"{moved / us / 1e6:5.2f} TB/s of activations and states, {2 * tokens * heads * dim * vdim / us / 1e6:6.2f} T multiply-adds/s")
 
 
+def bench_linear_attention(config, page: int) -> None:
+    """Linear attention with a matrix state, 8 heads of 128 by 256 (the sizes of ``bench.py --design segetar`` at width
+    2,048; as many multiply-adds as ``lightning`` above): a decay per token and key coordinate, and a fixed decay per head
+    with rotated queries and keys. One prompt of 2,048 tokens (chunks side by side), one of 128 (in a row), and a decode
+    step of 8 requests."""
+    from paged_kv_serving_b200.ops import mixer_ops
+
+    heads, dim, vdim = 8, 128, 256
+    qk, vg = heads * dim, heads * vdim
+    offsets = {"q": 0, "k": qk, "v": 2 * qk, "g": 2 * qk + vg}
+    decay = torch.linspace(0.96, 0.999, heads, device="cuda")
+    weight, bias = torch.ones((vdim,), device="cuda"), torch.full((qk,), 3.0, device="cuda")
+    freq = torch.tensor([10000.0 ** (-2.0 * i / dim) for i in range(dim // 2)], device="cuda")
+    for tokens, seqs in ((2048, 1), (128, 1), (8, 8)):
+        proj = [torch.randn((tokens, 2 * qk + 2 * vg), device="cuda") for _ in range(4)]
+        pre = [torch.randn((tokens, qk), device="cuda") for _ in range(4)]
+        state = torch.zeros((seqs, heads, vdim, dim), device="cuda")
+        starts = torch.arange(0, tokens + 1, tokens // seqs, device="cuda", dtype=torch.int32)
+        slots = torch.arange(seqs, device="cuda", dtype=torch.int32)
+        positions = (torch.arange(tokens, device="cuda", dtype=torch.int32) % (tokens // seqs)) + (1024 if seqs > 1 else 0)
+        forms = {
+            "a decay per token and key coordinate": lambda i: mixer_ops.linear_attention(
+                proj[i % 4], offsets, state, starts, slots, heads, dim, vdim, torch.bfloat16, decay_pre=pre[i % 4], decay_bias=bias,
+                inv_tau=1.0 / 16.0, q_scale=dim ** -0.5, norm_weight=weight),
+            "a fixed decay per head, rotated": lambda i: mixer_ops.linear_attention(
+                proj[i % 4], offsets, state, starts, slots, heads, dim, vdim, torch.bfloat16, head_decay=decay, k_scale=dim ** -0.5,
+                rot_dims=dim, freq=freq, positions=positions),
+        }
+        chunk = mixer_ops.linear_attention_chunk(tokens, seqs)
+        for name, fn in forms.items():
+            us = timed(fn)
+            moved = tokens * (2 * qk + 2 * vg) * 4 + tokens * vg * 2 + 2 * seqs * heads * vdim * dim * 4
+            print(f"linear attention, {name}, {tokens:5d} tokens in {seqs} sequences ({f'chunks of {chunk}' if chunk else 'in a row'}): "
+                  f"{us:7.1f} us, {moved / us / 1e6:5.2f} TB/s of activations and states, "
+                  f"{2 * tokens * heads * dim * vdim / us / 1e6:6.2f} T multiply-adds/s")
+
+
 def bench_sink_attention(config, page: int) -> None:
     """Attention over a window of 1,024 keys with 4 kept first tokens and a score cap, 16 query and 4 key/value
     heads: heads of 128 (tcgen05 for a prompt, the TMA-fed kernel for decode entries), and keys of 96 with values
@@ -319,7 +356,7 @@ def bench_sink_attention(config, page: int) -> None:
 def main() -> int:
     cases = {"gemm": None, "decode-gemm": None, "prefill-attention": bench_prefill_attention, "decode-attention": bench_decode_attention,
              "elementwise": bench_elementwise, "scan": bench_scan, "sink-attention": bench_sink_attention,
-             "lightning": bench_lightning}
+             "lightning": bench_lightning, "linear-attention": bench_linear_attention}
     parser = argparse.ArgumentParser(description=__doc__.splitlines()[0])
     parser.add_argument("cases", nargs="*", choices=[*cases, []], help="which kernels to time (default: all)")
     parser.add_argument("--preset", default="llama-3-8b")

@@ -2,11 +2,11 @@
 // (retention) or computed per token and key coordinate (gated linear attention), for a ragged batch
 // of portions of sequences. Per head, with q, k [dim], v [vdim] and the decay a [dim]:
 //   S_t = diag(a_t) S_{t-1} + k_t v_t^T,    o_t = S_t^T q_t
-// Everything here is float32. The projections arrive as float32 rows `proj [tokens, ld]`; what turns
-// them into the recurrence's inputs happens while a block stages them in shared memory:
+// Everything here is float32. The projections arrive as float32 rows `proj [tokens, ld]`; `prepare`
+// turns them into the recurrence's inputs in place, once per token:
 //   queries and keys: a rotation of the first `rot_dims` coordinates of a head by the token's
 //     position (coordinate i pairs with i + rot_dims / 2, angle = position * freq[i]), then a factor;
-//   the decay: a_t[d] = sigmoid(z_t[d] + bias[d]) ^ inv_tau = exp(inv_tau * log sigmoid), staged as
+//   the decay: a_t[d] = sigmoid(z_t[d] + bias[d]) ^ inv_tau = exp(inv_tau * log sigmoid), left as
 //     a_t[d] - 1 = expm1(inv_tau * log sigmoid) and applied as S + (a - 1) S: a decay close to 1 would
 //     round to 24 bits with an error that a long memory adds up token after token, its small part
 //     does not; or the head's fixed number.
@@ -64,17 +64,41 @@ __device__ __forceinline__ int la_entry_of_slot(const int32_t* __restrict__ seq_
 // log(sigmoid(z)) without overflow: min(z, 0) - log(1 + exp(-|z|))
 __device__ __forceinline__ float la_log_sigmoid(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
-// One staged coordinate of a query or key head: rotated by the token's position where it belongs
-// to the rotated part. `x` points at the head's first coordinate.
-__device__ __forceinline__ float la_rotated(const float* __restrict__ x, int d, int rot_dims, const float* __restrict__ freq,
-                                            float pos) {
-  if (d >= rot_dims) return x[d];
-  const int half = rot_dims >> 1;
-  const int i = d < half ? d : d - half;
-  const float u = x[i], v = x[i + half];
-  float sn, cs;
-  sincosf(pos * freq[i], &sn, &cs);
-  return d < half ? u * cs - v * sn : v * cs + u * sn;
+// One block a token: queries and keys rotated and scaled in place, the decays' pre-activations replaced
+// by the decays minus one.
+__global__ void __launch_bounds__(128)
+la_prepare_kernel(float* __restrict__ proj, float* __restrict__ a_pre, LaParams p) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
+  const int t = blockIdx.x;
+  float* row = proj + (size_t)t * p.ld;
+  const int n = p.heads * p.dim, half = p.rot_dims >> 1;
+  const float pos = p.rot_dims ? (float)p.positions[t] : 0.0f;
+  const bool touch = p.rot_dims > 0 || p.q_scale != 1.0f || p.k_scale != 1.0f;
+  if (touch) {
+    for (int idx = threadIdx.x; idx < n; idx += blockDim.x) {
+      const int head = idx / p.dim, d = idx - head * p.dim;
+      float* q = row + p.q_off + (size_t)head * p.dim;
+      float* k = row + p.k_off + (size_t)head * p.dim;
+      if (d < half) {                                 // this thread turns the pair (d, d + half) of both
+        float sn, cs;
+        sincosf(pos * p.freq[d], &sn, &cs);
+        const float qu = q[d], qv = q[d + half], ku = k[d], kv = k[d + half];
+        q[d] = (qu * cs - qv * sn) * p.q_scale;
+        q[d + half] = (qv * cs + qu * sn) * p.q_scale;
+        k[d] = (ku * cs - kv * sn) * p.k_scale;
+        k[d + half] = (kv * cs + ku * sn) * p.k_scale;
+      } else if (d >= p.rot_dims) {
+        q[d] *= p.q_scale;
+        k[d] *= p.k_scale;
+      }
+    }
+  }
+  if (a_pre) {
+    float* z = a_pre + (size_t)t * p.a_ld;
+    for (int idx = threadIdx.x; idx < n; idx += blockDim.x)
+      z[idx] = expm1f(la_log_sigmoid(z[idx] + (p.a_bias ? p.a_bias[idx] : 0.0f)) * p.inv_tau);
+  }
 }
 
 template <int L, int R, int STAGE, int MODE, bool GATED>
@@ -87,6 +111,8 @@ la_scan_kernel(const float* __restrict__ proj, LaParams p, float* __restrict__ s
   constexpr int COLS = LA_THREADS / L;
   constexpr int DP = L * R;                       // dim rounded up to what the lanes hold
   constexpr int R4 = R / 4;
+  constexpr int PER = STAGE * DP / LA_THREADS;    // staged entries per thread and operand
+  constexpr int BATCH = PER < 8 ? PER : 8;
   __shared__ __align__(16) float q_s[MODE == LA_LOCAL ? 1 : STAGE][DP];
   __shared__ __align__(16) float k_s[STAGE][DP];
   __shared__ __align__(16) float a_s[GATED ? STAGE : 1][DP];
@@ -139,23 +165,28 @@ la_scan_kernel(const float* __restrict__ proj, LaParams p, float* __restrict__ s
   for (int base = 0; base < count; base += STAGE) {
     const int n = min(STAGE, count - base);
     __syncthreads();                              // the tokens staged before are consumed and flushed
-    for (int idx = threadIdx.x; idx < STAGE * DP; idx += LA_THREADS) {
-      const int j = idx / DP, d = idx - j * DP;
-      float kk = 0.0f, qq = 0.0f, aa = 0.0f;       // (aa: the decay minus one)
-      if (j < n && d < dim) {
-        const int token = start + base + j;
-        const float* row = proj + (size_t)token * p.ld + (size_t)head * dim;
-        const float pos = p.rot_dims ? (float)p.positions[token] : 0.0f;
-        kk = la_rotated(row + p.k_off, d, p.rot_dims, p.freq, pos) * p.k_scale;
-        if (MODE != LA_LOCAL) qq = la_rotated(row + p.q_off, d, p.rot_dims, p.freq, pos) * p.q_scale;
-        if (GATED) {
-          const float z = p.a_pre[(size_t)token * p.a_ld + (size_t)head * dim + d] + (p.a_bias ? p.a_bias[head * dim + d] : 0.0f);
-          aa = expm1f(la_log_sigmoid(z) * p.inv_tau);
-        }
+#pragma unroll 1
+    for (int i0 = 0; i0 < PER; i0 += BATCH) {
+      float qv[BATCH], kv[BATCH], av[BATCH];          // several loads in flight per operand
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const int idx = threadIdx.x + (i0 + i) * LA_THREADS;
+        const int j = idx / DP, d = idx - j * DP;
+        const bool there = j < n && d < dim;
+        const size_t token = (size_t)(start + base + (there ? j : 0));
+        const float* row = proj + token * p.ld + (size_t)head * dim + (there ? d : 0);
+        kv[i] = there ? row[p.k_off] : 0.0f;
+        qv[i] = (MODE != LA_LOCAL && there) ? row[p.q_off] : 0.0f;
+        av[i] = (GATED && there) ? p.a_pre[token * p.a_ld + (size_t)head * dim + d] : 0.0f;       // the decay minus one
       }
-      k_s[j][d] = kk;
-      if (MODE != LA_LOCAL) q_s[j][d] = qq;
-      if (GATED) a_s[j][d] = aa;
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const int idx = threadIdx.x + (i0 + i) * LA_THREADS;
+        const int j = idx / DP, d = idx - j * DP;
+        k_s[j][d] = kv[i];
+        if (MODE != LA_LOCAL) q_s[j][d] = qv[i];
+        if (GATED) a_s[j][d] = av[i];
+      }
     }
     for (int idx = threadIdx.x; idx < n * COLS; idx += LA_THREADS) {
       const int j = idx / COLS, c = idx - j * COLS;
@@ -328,7 +359,8 @@ static int la_launch(const float* proj, const LaParams& p, float* state, const i
 }
 
 // proj float32 [tokens, ld]: q and k [heads, dim] at q_off and k_off, v and the output gate's
-// pre-activation [heads, vdim] at v_off and g_off. With a_pre, float32 rows of [heads, dim] with stride
+// pre-activation [heads, vdim] at v_off and g_off; the queries' and keys' columns are overwritten
+// (rotated and scaled). With a_pre (overwritten too), float32 rows of [heads, dim] with stride
 // a_ld hold the decays' pre-activations (a_bias float32 [heads * dim] or null is added; the decay is
 // their sigmoid to the power inv_tau); without, head_decay float32 [heads] holds a fixed decay per head.
 // freq float32 [rot_dims / 2] and positions int32 [tokens] when rot_dims > 0. state float32 [slots,
@@ -338,7 +370,7 @@ static int la_launch(const float* proj, const LaParams& p, float* state, const i
 // launch; chunk > 0: chunks of that many tokens side by side, with chunk_state float32 [tokens /
 // chunk + seqs, heads, vdim, dim] and (with a_pre) chunk_decay float32 [tokens / chunk + seqs, heads,
 // dim] as their working memory.
-PKV_EXPORT int pkv_linear_attention(const float* proj, int ld, int q_off, int k_off, int v_off, int g_off, const float* a_pre,
+PKV_EXPORT int pkv_linear_attention(float* proj, int ld, int q_off, int k_off, int v_off, int g_off, float* a_pre,
                                     int a_ld, const float* a_bias, float inv_tau, const float* head_decay, float q_scale, float k_scale,
                                     int rot_dims, const float* freq, const int32_t* positions, const float* norm_weight,
                                     float eps, float out_factor, float* state, const int32_t* seq_starts,
@@ -356,6 +388,10 @@ PKV_EXPORT int pkv_linear_attention(const float* proj, int ld, int q_off, int k_
              heads, dim, vdim, seqs, chunk};
   cudaStream_t s = (cudaStream_t)stream;
   int rc;
+  if (gated || rot_dims > 0 || q_scale != 1.0f || k_scale != 1.0f) {
+    rc = launch_kernel(la_prepare_kernel, dim3(tokens), dim3(128), 0, s, true, 0, proj, a_pre, p);
+    if (rc != 0) return rc;
+  }
 #define PKV_LA(L, R, STAGE)                                                                                                  \
   rc = gated ? la_launch<L, R, STAGE, true>(proj, p, state, seq_starts, state_slots, scratch, tokens, chunk_state, chunk_decay, s) \
              : la_launch<L, R, STAGE, false>(proj, p, state, seq_starts, state_slots, scratch, tokens, chunk_state, chunk_decay, s)

@@ -420,6 +420,22 @@ __global__ void gated_bias_act_kernel(const X* __restrict__ gu, int ld, int up_a
   out[(size_t)t * n + c] = from_float<X>(activate(g, act) * u);
 }
 
+__global__ void gated_bias_act_bf16x8_kernel(const bf16* __restrict__ gu, int ld, int up_at, const float* __restrict__ gate_bias,
+                                             const float* __restrict__ up_bias, bf16* __restrict__ out, int tokens, int n, int act) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
+  const int per_row = n >> 3;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)tokens * per_row) return;
+  const int t = (int)(i / per_row), c = (int)(i - (long long)t * per_row) << 3;
+  Pack8 g = load8(gu + (size_t)t * ld + c);
+  const Pack8 u = load8(gu + (size_t)t * ld + up_at + c);
+#pragma unroll
+  for (int k = 0; k < 8; ++k)
+    g.v[k] = activate(g.v[k] + (gate_bias ? gate_bias[c + k] : 0.0f), act) * (u.v[k] + (up_bias ? up_bias[c + k] : 0.0f));
+  store8(out + (size_t)t * n + c, g);
+}
+
 // hidden[t] += delta[t] (when given); out[t] = [hidden[t] | other[t]] in the type of out: the
 // stream beside a second float32 matrix of the same shape, as the operand of one product.
 template <typename D, typename O>
@@ -684,6 +700,9 @@ PKV_EXPORT int pkv_gated_bias_act(const void* gu, int dtype, int ld, int up_at, 
   if (dtype == PKV_F32)
     return launch_kernel(gated_bias_act_kernel<float>, dim3(blocks_for(total, 256)), dim3(256), 0, s, true, 0, (const float*)gu, ld,
                          up_at, gate_bias, up_bias, (float*)out, tokens, n, act);
+  if (dtype == PKV_BF16 && n % 8 == 0 && ld % 8 == 0 && up_at % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0)
+    return launch_kernel(gated_bias_act_bf16x8_kernel, dim3(blocks_for(total / 8, 256)), dim3(256), 0, s, true, 0, (const bf16*)gu, ld,
+                         up_at, gate_bias, up_bias, (bf16*)out, tokens, n, act);
   if (dtype == PKV_BF16)
     return launch_kernel(gated_bias_act_kernel<bf16>, dim3(blocks_for(total, 256)), dim3(256), 0, s, true, 0, (const bf16*)gu, ld,
                          up_at, gate_bias, up_bias, (bf16*)out, tokens, n, act);

@@ -1,6 +1,6 @@
 """Prefill and decode throughput of one architecture at layer sizes of a real model (random
 weights), with the time of every kernel of a step against its roofline. ``bench.py --design``
-runs it for the Revupel, the Tiburax or the Rodelix design and, at equal sizes, for the models it is compared with.
+runs it for the Revupel, the Tiburax, the Rodelix or the Segetar design and, at equal sizes, for the models it is compared with.
 
 A step runs through ``ModelRunner.step``. For the kernel table one eager step is run with every
 kernel call of ``ops`` / ``ops.mixer_ops`` and every library product bracketed by CUDA events on
@@ -14,7 +14,8 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-__all__ = ["RODELIX_SIZES", "SIZES", "TIBURAX_SIZES", "llama_like", "measure", "revupel_config", "rodelix_config", "tiburax_config"]
+__all__ = ["RODELIX_SIZES", "SEGETAR_SIZES", "SIZES", "TIBURAX_SIZES", "llama_like", "measure", "revupel_config", "rodelix_config",
+           "segetar_config", "tiburax_config"]
 
 #: name -> sizes of a Revupel model whose layers resemble a served model's (latent attention of
 #: the kind with a compressed cache, an mLSTM block, eight experts of which two run, a dense block)
@@ -95,6 +96,44 @@ def rodelix_config(size: str) -> dict:
             "logit_softcap": 30.0, "layers": layers}
 
 
+#: name -> sizes of a Segetar model at the same width and layer count: a Mamba block, window attention (grouped keys,
+#: heads of 128, window 1,024) beside gated linear attention (keys of 128, values of 256), window attention beside
+#: retention, a Mamba block again; a dense gated feed-forward and eight gated experts of which two run, chosen within
+#: two of four groups; the four layers are one span with a pass input in front
+SEGETAR_SIZES = {
+    "1b": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, r_heads=8, r_dim=128, r_vdim=256, rank=16,
+               inner=4096, state=16, dt_rank=128, ff=5632, experts=8, top=2, expert_ff=2048, vocab=32000),
+    "7b": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, r_heads=16, r_dim=128, r_vdim=256, rank=32,
+               inner=8192, state=16, dt_rank=256, ff=9728, experts=8, top=2, expert_ff=3584, vocab=32000),
+}
+
+
+def segetar_config(size: str) -> dict:
+    z = SEGETAR_SIZES[size]
+
+    def attention(rotated: bool) -> dict:
+        side = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+                "mask": {"size": z["window"]}}
+        if rotated:
+            side["rot"] = {"base": 500000.0, "dims": z["dim"]}
+        return side
+
+    decays = [1.0 - 2.0 ** (-5.0 - 3.0 * a / max(z["r_heads"] - 1, 1)) for a in range(z["r_heads"])]
+    gated = {"type": "parallel", "mixer": {
+        "left": attention(True), "right": {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"], "tau": 16.0, "rank": z["rank"]},
+        "left_scale": 1.0, "right_scale": 0.5}}
+    retentive = {"type": "parallel_2", "mixer": {
+        "left": attention(False), "right": {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"], "decay": decays,
+                                            "rot": {"base": 10000.0, "dims": z["r_dim"]}}}}
+    recurrent = {"type": "mamba1", "mixer": {"inner": z["inner"], "state": z["state"], "dt_rank": z["dt_rank"], "conv": 4}}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    layers = [{**recurrent, "mlp": dense}, {**gated, "mlp": moe}, {**retentive, "mlp": moe}, {**recurrent, "mlp": moe}]
+    return {"architecture": "Segetar", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "loop": {"start": 0, "stop": len(layers), "times": 1}, "layers": layers}
+
+
 def llama_like(size: str) -> dict:
     """The Llama-style decoder at the same width, layer count and head count; its gated
     feed-forward has the parameter count of the dense block above."""
@@ -148,7 +187,8 @@ class _KernelTimes:
         for name in ("bias_act", "residual_add", "act_times_table", "route_top", "expert_act", "conv_residual", "mlstm",
                      "latent_prepare", "latent_attention", "latent_attention_mma", "norm_residual", "expert_gated_act",
                      "qkv_prepare", "attention_sink", "attention_sink_mma", "selective_scan", "layer_norm_step", "token_shift",
-                     "lightning", "softcap"):
+                     "lightning", "softcap", "linear_attention", "route_scored", "gated_bias_act", "pair_rows", "assign_bias",
+                     "combine_pair", "head_gate"):
             self._wrap(mixer_ops, name, "kernel")
         self._wrap(gemm, "matmul", "product")
         self._wrap(torch, "bmm", "product")
@@ -266,6 +306,12 @@ def measure(config: dict, peaks: dict, *, prefill_tokens: int = 2048, batch: int
         heads, dim, vdim = args[8], args[9], args[10]
         return _bytes_of((args[0], out)) + out.numel() * 8, 4.0 * args[0].shape[0] * heads * dim * vdim
 
+    def linear_attention_cost(args, out):
+        # linear_attention(proj, offsets, state, starts, slots, heads, dim, vdim, out_dtype, ...)
+        heads, dim, vdim = args[5], args[6], args[7]
+        return _bytes_of((args[0], out)) + out.numel() * 8, 4.0 * args[0].shape[0] * heads * dim * vdim
+
+    cost["linear_attention"] = linear_attention_cost
     cost["lightning"] = lightning_cost
     cost.update({"attention_sink": sink_cost, "attention_sink_mma": sink_cost, "selective_scan": scan_cost})
     cost.update({"latent_attention": latent_cost, "latent_attention_mma": latent_cost,

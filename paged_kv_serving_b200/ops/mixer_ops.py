@@ -859,7 +859,8 @@ def linear_attention(proj: torch.Tensor, offsets: dict[str, int], state: torch.T
     freq[i]``), then multiplied by ``q_scale`` / ``k_scale``. ``state`` float32 ``[slots, heads, vdim, dim]`` is read and
     brought up to date. Returns, per head, the outputs divided by their root mean square over ``vdim``, times
     ``norm_weight`` (float32 ``[vdim]`` or none), the SiLU of the gate and ``out_factor``: ``[tokens, heads * vdim]`` in
-    ``out_dtype``, or written into ``out`` (a view of that shape whose rows may have a stride)."""
+    ``out_dtype``, or written into ``out`` (a view of that shape whose rows may have a stride). The kernel prepares its
+    inputs in place: the query and key columns of ``proj`` and all of ``decay_pre`` are overwritten."""
     _need(proj, torch.float32, "proj"); _need(state, torch.float32, "state")
     tokens, ld = proj.shape
     if state.shape[1:] != (heads, vdim, dim):
@@ -907,5 +908,6 @@ def linear_attention(proj: torch.Tensor, offsets: dict[str, int], state: torch.T
               float(eps), float(out_factor), _ptr(state), _ptr(seq_starts), _ptr(state_slots), _ptr(scratch),
               c_void_p(out.data_ptr()), dtype_code(out_dtype), out_ld, tokens, seqs, heads, dim, vdim, chunk,
               _ptr(chunk_state), _ptr(chunk_decay), _stream()), "linear_attention")
-    ops.LAUNCHES["count"] += 3 if chunk else 1
+    prepared = decay_pre is not None or rot_dims or q_scale != 1.0 or k_scale != 1.0
+    ops.LAUNCHES["count"] += (3 if chunk else 1) + (1 if prepared else 0)
     return out
