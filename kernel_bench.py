@@ -273,7 +273,7 @@ def bench_linear_attention(config, page: int) -> None:
         forms = {
             "a decay per token and key coordinate": lambda i: mixer_ops.linear_attention(
                 proj[i % 4], offsets, state, starts, slots, heads, dim, vdim, torch.bfloat16, decay_pre=pre[i % 4], decay_bias=bias,
-                inv_tau=1.0 / 16.0, q_scale=dim ** -0.5, norm_weight=weight),
+                inv_tau=1.0 / 8.0, q_scale=dim ** -0.5, norm_weight=weight),
             "a fixed decay per head, rotated": lambda i: mixer_ops.linear_attention(
                 proj[i % 4], offsets, state, starts, slots, heads, dim, vdim, torch.bfloat16, head_decay=decay, k_scale=dim ** -0.5,
                 rot_dims=dim, freq=freq, positions=positions),

@@ -115,13 +115,13 @@ def segetar_config(size: str) -> dict:
         side = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
                 "mask": {"size": z["window"]}}
         if rotated:
-            side["rot"] = {"base": 500000.0, "dims": z["dim"]}
+            side["rot"] = {"base": 1000000.0, "dims": z["dim"]}
         return side
 
     decays = [1.0 - 2.0 ** (-5.0 - 3.0 * a / max(z["r_heads"] - 1, 1)) for a in range(z["r_heads"])]
     gated = {"type": "parallel", "mixer": {
-        "left": attention(True), "right": {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"], "tau": 16.0, "rank": z["rank"]},
-        "left_scale": 1.0, "right_scale": 0.5}}
+        "left": attention(True), "right": {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"], "tau": 8.0, "rank": z["rank"]},
+        "left_scale": 1.0, "right_scale": 0.7}}
     retentive = {"type": "parallel_2", "mixer": {
         "left": attention(False), "right": {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"], "decay": decays,
                                             "rot": {"base": 10000.0, "dims": z["r_dim"]}}}}

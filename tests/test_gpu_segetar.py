@@ -74,7 +74,7 @@ CONFIG_A = _model([_layer(_mamba(), 72),
 #: "B": heads of 64 (what the tcgen05 and TMA kernels take) with windows that straddle pages of 16, every query
 #: head with keys of its own in one layer and one key head for all in the other, the whole model looped twice from
 #: its first layer, experts in one group.
-CONFIG_B = _model([_layer(_parallel(_attention(2, 1, 64, 64, size=40, rot=(64, 500000.0)), 2, 32, 16, 16.0, 8, 1.2, 0.5), _moe(4, 2, 32, 1, 1, 1.5)),
+CONFIG_B = _model([_layer(_parallel(_attention(2, 1, 64, 64, size=44, rot=(64, 250000.0)), 2, 32, 16, 12.0, 8, 1.1, 0.6), _moe(4, 2, 32, 1, 1, 1.4)),
                    _layer(_parallel_2(_attention(2, 2, 64, 64, size=21), 1, 32, 32, (0.97,), (32, 50.0)), 48),
                    _layer(_mamba(64, 16, 8, 3), _moe(4, 1, 16, 2, 2, 1.0))],
                   vocab=97, width=128, eps=1e-6, loop=(0, 3, 2))
