@@ -65,10 +65,11 @@ def _model(layers, vocab=150, width=64, eps=1e-5, loop=None):
     return config
 
 
-#: "A": every kind of layer; a window of 20 on pages of 8; grouped keys; a rotation of part of a head; two layers
-#: behind the first run three times.
+#: "A": every kind of layer; a window of 20 on pages of 8; grouped keys of 32 with values of 16 (sizes the mma.sync
+#: attention kernel takes) and keys of 24 (the general kernel); a rotation of part of a head; two layers behind the first
+#: run three times.
 CONFIG_A = _model([_layer(_mamba(), 72),
-                   _layer(_parallel(_attention(4, 2, 16, 24, size=20, rot=(8, 10000.0))), _moe()),
+                   _layer(_parallel(_attention(4, 2, 32, 16, size=20, rot=(8, 10000.0))), _moe()),
                    _layer(_parallel_2(_attention(2, 1, 24, 16, size=13)), _moe(8, 3, 16, 2, 1, 0.9)),
                    _layer(_mamba(24, 3, 2, 2), None)], loop=(1, 3, 3))
 #: "B": heads of 64 (what the tcgen05 and TMA kernels take) with windows that straddle pages of 16, every query
