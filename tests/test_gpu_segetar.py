@@ -650,3 +650,80 @@ def test_command_line_checkpoint_generation_and_trace_program(tmp_path):
     close(read(0), want_a[[0, 20]], "float32", "trace step 0")
     close(read(1), want_b[[3]], "float32", "trace step 1")
     close(read(2), np.stack([want_b[11], want_a[29]]), "float32", "trace step 2")
+
+
+# --- seeded random configurations ---------------------------------------------------------------------
+
+
+def _random_config(rng):
+    """A configuration drawn at random within the design's bounds: layer order, every size, windows, rotated parts,
+    decays, router groups, a looped span anywhere or none."""
+    width = int(rng.choice([32, 48, 64, 96, 128]))
+
+    def attention(rotated):
+        dim = int(rng.choice([6, 8, 16, 32, 64]))
+        vdim = int(rng.choice([dim, dim, 8, 16, 24]))
+        kv = int(rng.choice([1, 2, 3]))
+        heads = kv * int(rng.choice([1, 2, 4]))
+        size = int(rng.choice([1, 3, 16, 17, 33, 64, 500]))
+        rot = (int(rng.choice([2, dim // 2 * 2, dim])), float(rng.choice([50.0, 10000.0, 1e6]))) if rotated and rng.random() < 0.8 else None
+        return _attention(heads, kv, dim, vdim, size=size if rng.random() < 0.9 else None, rot=rot, scale=float(rng.choice([dim ** -0.5, 0.1, 0.3])))
+
+    def mixer():
+        kind = rng.choice(["mamba1", "parallel", "parallel_2"])
+        if kind == "mamba1":
+            return _mamba(int(rng.choice([16, 24, 40, 64])), int(rng.choice([1, 4, 6, 16, 24])), int(rng.choice([1, 3, 8])), int(rng.choice([1, 2, 3, 4])))
+        heads, dim, vdim = int(rng.choice([1, 2, 4])), int(rng.choice([4, 12, 16, 32, 48])), int(rng.choice([4, 10, 16, 32]))
+        if kind == "parallel":
+            return _parallel(attention(True), heads, dim, vdim, float(rng.choice([1.0, 8.0, 16.0])), int(rng.choice([1, 4, 16])),
+                             float(rng.choice([0.5, 1.0, 1.2])), float(rng.choice([0.5, 1.0, 2.0])))
+        decay = [float(d) for d in rng.choice([0.5, 0.9, 0.984375, 0.999, 1.0], size=heads)]
+        rot = (int(rng.choice([2, dim // 2 * 2, dim])), float(rng.choice([100.0, 1e6]))) if rng.random() < 0.7 else None
+        return _parallel_2(attention(False), heads, dim, vdim, decay, rot)
+
+    def feed_forward():
+        kind = rng.choice(["dense", "moe", "none"], p=[0.35, 0.5, 0.15])
+        if kind == "none":
+            return None
+        if kind == "dense":
+            return int(rng.choice([16, 40, 72]))
+        count = int(rng.choice([1, 2, 4]))
+        per = int(rng.choice([1, 2, 4]))
+        keep = int(rng.integers(1, count + 1))
+        top = int(rng.integers(1, per * keep + 1))
+        return _moe(count * per, top, int(rng.choice([8, 16, 24])), count, keep, float(rng.choice([1.0, 1.5, 2.5])))
+
+    layers = [_layer(mixer(), feed_forward()) for _ in range(int(rng.integers(1, 5)))]
+    loop = None
+    if rng.random() < 0.7:
+        start = int(rng.integers(0, len(layers)))
+        loop = (start, int(rng.integers(start + 1, len(layers) + 1)), int(rng.choice([1, 2, 3])))
+    return _model(layers, vocab=int(rng.choice([50, 97, 600])), width=width, eps=float(rng.choice([1e-6, 1e-5])), loop=loop)
+
+
+@pytest.mark.parametrize("seed", range(2000, 2016))
+def test_seeded_random_configurations_in_random_cuts(seed):
+    rng = np.random.default_rng(seed)
+    config = _random_config(rng)
+    tensors = random_tensors(config, seed=seed, scale=1.2)
+    count = int(rng.choice([40, 90, 200, 330]))
+    tokens = tokens_for(config, count, seed=seed + 1)
+    want = plain_logits(config, tensors, tokens)
+    page = int(rng.choice([8, 16, 16, 32]))
+    cuts = [int(c) for c in sorted(rng.choice(np.arange(1, count), size=min(6, count - 1), replace=False))] + [count]
+    decoded = [bool(rng.random() < 0.5) for _ in cuts]
+    for dtype in DTYPES:
+        session = session_for(config, tensors, dtype, max_tokens=count + 64, page=page)
+        rows, at = [], 0
+        for cut, alone in zip(cuts, decoded):
+            last = cut - 8 if alone and cut - at > 30 else cut         # the last eight tokens of some portions one by one
+            part = tokens[at:last]
+            rows.append(session.step([{"id": "r", "tokens": part, "want": list(range(len(part)))}]))
+            rows += [session.step([{"id": "r", "tokens": [t], "want": [0]}]) for t in tokens[last:cut]]
+            at = cut
+        got = np.concatenate(rows)
+        error = row_errors(got, want)
+        if dtype == "float32":       # (a router's near tie may move a single row a little further than rounding does)
+            assert float(np.median(error)) <= 2e-5 and float(error.max()) <= 1e-3, f"seed {seed}: rows off by up to {error.max():.3e}"
+        else:
+            assert float(np.median(error)) <= 0.06 and float(error.max()) <= 1.5, f"seed {seed}: rows off by up to {error.max():.3e}"
