@@ -537,6 +537,72 @@ def test_query_and_key_preparation_with_biases_joint_norm_and_neighbour_pairs():
     assert torch.equal(qkv[:, part.gate_at:part.gate_at + H].cpu(), (h.cuda() @ part.qkv.T)[:, part.gate_at:part.gate_at + H].cpu())
 
 
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16))
+def test_small_kernels_alone_gated_activation_head_gate_and_the_two_combinations(dtype):
+    from paged_kv_serving_b200.ops import mixer_ops
+
+    rng = torch.Generator().manual_seed(61)
+    loose = dtype == torch.bfloat16
+    # the middle of a gated feed-forward with biases: widths that do and do not take the 16-byte form
+    for tokens, n, up_at in ((7, 24, 24), (5, 13, 16)):
+        gu = torch.randn((tokens, up_at + n + 3), generator=rng).to(dtype)
+        bg, bu = torch.randn((n,), generator=rng), torch.randn((n,), generator=rng)
+        got = mixer_ops.gated_bias_act(gu.cuda(), up_at, n, bg.cuda(), bu.cuda(), "gelu_tanh").cpu().double()
+        g, u = gu.double()[:, :n] + bg, gu.double()[:, up_at:up_at + n] + bu
+        want = plain.gelu_tanh(g) * u
+        assert (got - want).abs().max() <= (0.02 if loose else 1e-5) * want.abs().max()
+        bare = mixer_ops.gated_bias_act(gu.cuda(), up_at, n, None, None, "silu").cpu().double()
+        want = plain.silu(gu.double()[:, :n]) * gu.double()[:, up_at:up_at + n]
+        assert (bare - want).abs().max() <= (0.02 if loose else 1e-5) * want.abs().max()
+    # one sigmoid gate per token and head, a factor, and a destination whose rows have a stride of their own
+    heads, vdim, tokens = 3, 10, 6
+    x = torch.randn((tokens, heads * vdim), generator=rng).to(dtype)
+    wide = torch.randn((tokens, 40), generator=rng).to(dtype).cuda()                  # the gates lie at columns 33..35
+    out = torch.zeros((tokens, heads * vdim + 7), dtype=dtype, device="cuda")
+    view = mixer_ops.head_gate(x.cuda(), wide[:, 33:36], heads, vdim, 1.3, out=out[:, 2:2 + heads * vdim])
+    want = (x.double().view(tokens, heads, vdim) * torch.sigmoid(wide[:, 33:36].cpu().double())[:, :, None] * 1.3).reshape(tokens, -1)
+    assert (view.cpu().double() - want).abs().max() <= (0.02 if loose else 1e-5) * want.abs().max()
+    assert (out[:, :2] == 0).all() and (out[:, 2 + heads * vdim:] == 0).all()
+    same = x.clone().cuda()
+    assert mixer_ops.head_gate(same, None, heads, vdim, 0.5) is same and (same.cpu().double() - 0.5 * x.double()).abs().max() <= 0.01
+    if dtype == torch.float32:
+        # two updates become one: with factors, or each divided by its own root mean square and weighted
+        a, b = torch.randn((9, 52), generator=rng), 5.0 * torch.randn((9, 52), generator=rng)
+        wa, wb = torch.randn((52,), generator=rng), torch.randn((52,), generator=rng)
+        got = mixer_ops.combine_pair(a.cuda(), b.cuda(), 1.2, 0.5).cpu().double()
+        assert (got - (1.2 * a.double() + 0.5 * b.double())).abs().max() <= 1e-5
+        got = mixer_ops.combine_pair(a.cuda(), b.cuda(), 0.5, 0.5, norm_weights=(wa.cuda(), wb.cuda()), eps=1e-5).cpu().double()
+        want = 0.5 * (plain.unit_rms(a.double(), 1e-5) * wa + plain.unit_rms(b.double(), 1e-5) * wb)
+        assert (got - want).abs().max() <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_pass_input_part_alone(dtype):
+    """The stream takes a pending update, is laid beside the model's input, goes through the product and gets the
+    pass's vector: in place, and only the asked pass's row of the vectors is used."""
+    from paged_kv_serving_b200.parts import PassInput
+
+    rng = torch.Generator().manual_seed(71)
+    width, passes, tokens = 40, 3, 11
+    part = PassInput(width, passes)
+    compute = torch.float32 if dtype == "float32" else torch.bfloat16
+    mix = (torch.randn((width, 2 * width), generator=rng) / 6.0).to(torch.bfloat16)
+    step = torch.randn((passes, width), generator=rng).to(torch.bfloat16)
+    part.load({"mix": mix.to(compute).cuda(), "step": step.float().cuda()})
+    hidden = torch.randn((tokens, width), generator=rng)
+    pending = torch.randn((tokens, width), generator=rng)
+    first = torch.randn((tokens, width), generator=rng)
+    for number, update in ((0, None), (2, pending)):
+        stream = hidden.clone().cuda()
+        part.forward(stream, update.cuda() if update is not None else None, first.cuda(), number)
+        x = hidden.double() + (update.double() if update is not None else 0.0)
+        want = torch.cat([x, first.double()], dim=-1) @ mix.double().T + step.double()[number]
+        gap = (stream.cpu().double() - want).abs().max() / want.abs().max()
+        assert gap <= (1e-5 if dtype == "float32" else 0.02), f"pass {number}: off by {gap:.3e}"
+    with pytest.raises(ValueError):
+        part.forward(hidden.clone().cuda(), None, first.cuda(), 3)
+
+
 # --- greedy generation through the entry point and the scheduler ------------------------------------
 
 
